@@ -1,0 +1,132 @@
+/*
+ * q4fc_b200 -- C-ABI of the B200 (sm_100a) quantized fully-connected path.
+ *
+ * Drop-in boundary for the Q4_0 / Q4_1 FC of usstq/llama.cl: the entry points
+ * below are what a binding of that project's FC ops would call instead of its
+ * CPU code.  Plain pointers and sizes only; every pointer is a DEVICE pointer
+ * unless stated otherwise; every call is asynchronous on `stream` and
+ * allocates nothing.  All functions return 0 on success or a Q4FC_E* code and
+ * never throw or abort; q4fc_last_error() gives the detail text of the last
+ * failure on the calling thread.
+ *
+ * Packed weight tensor (identical, byte for byte, to the reference's):
+ *   int8 [Ng][Kg][BS],  Ng = ceil(N/32), Kg = ceil(K/G), one block = 32
+ *   columns x G k:  G/8 rows of 128 bytes (byte n*4 + (k&3) of row k>>3 holds
+ *   k in its low nibble when ((k>>2)&1)==0, else in its high nibble), then
+ *   32 fp16 scales, then (Q4_1 only) 32 fp16 minima.
+ *   BS = 16*G + 64 (Q4_0) or 16*G + 128 (Q4_1): 576 / 2112 / 640 / 2176.
+ *   (reference: ops/op_fc.hpp:14-24, 39-48, 64-71)
+ */
+#ifndef Q4FC_B200_H
+#define Q4FC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with hidden visibility */
+#endif
+
+/* cudaStream_t, passed as an opaque pointer so that this header needs no CUDA include */
+typedef void* q4fc_stream_t;
+
+enum {
+    Q4FC_Q4_0 = 0, /* symmetric, levels -7..7, no minimum   (ops/op_fc.hpp:64)  */
+    Q4FC_Q4_1 = 1  /* asymmetric, levels 0..15 + minimum    (ops/op_fc.hpp:14)  */
+};
+
+enum {
+    Q4FC_OK = 0,
+    Q4FC_EINVAL = 1,    /* bad size, null pointer, N not covered by Ng, K not covered by Kg */
+    Q4FC_EVARIANT = 2,  /* (qtype, group_k) is not one of the four block types */
+    Q4FC_EALIGN = 3,    /* a pointer or leading dimension misses its alignment */
+    Q4FC_EWORKSPACE = 4,/* workspace missing or smaller than q4fc_fc_workspace_bytes() */
+    Q4FC_ECUDA = 5,     /* a CUDA runtime call failed (launch, attribute) */
+    Q4FC_EDEVICE = 6,   /* a kernel reported a bounded wait that ran out */
+    Q4FC_ELIMIT = 7     /* size beyond a stated maximum of the entry point */
+};
+
+/* flags of q4fc_fc* */
+enum {
+    /* Q4_0 only: sign-extend the stored nibble.  Off by default because the
+     * reference reads it unsigned (ops/op_fc.hpp:95-106, 364-376) and parity
+     * is defined against that. */
+    Q4FC_FLAG_NIBBLE_SIGNED = 1u,
+    /* Launch with programmatic stream serialization: the kernel may start
+     * while its predecessor on the stream drains; it touches activations,
+     * outputs and workspace only after the predecessor has completed, and
+     * streams weights before that.  Use only when the predecessor does not
+     * write this call's weights. */
+    Q4FC_FLAG_PDL = 2u
+};
+
+int q4fc_version(void);
+const char* q4fc_strerror(int code);
+const char* q4fc_last_error(void);
+
+/* Block size in bytes, or -1 for an unknown variant.  (sizeof(q4_block), ops/op_fc.hpp:109) */
+int q4fc_block_bytes(int qtype, int group_k);
+/* Recover (qtype, group_k) from the last dimension of a packed tensor. */
+int q4fc_infer_variant(int block_bytes, int* qtype, int* group_k);
+
+/* Replaces offline_FC_quant_Q4A (ops/op_fc.hpp:151-219; old extension
+ * FC_quant_Q4A, ext/llama_ext.cpp:405-471).
+ * w: fp32 [N][K] row-major (16-byte aligned, K % 4 == 0).  wq: [Ng][Kg][BS].
+ * Bit-exact with the reference for K % group_k == 0.  Columns n >= N get zero
+ * scale, minimum and nibbles (the reference leaves those nibbles
+ * uninitialised); a ragged last K group is scanned over its valid part only. */
+int q4fc_pack(const float* w, int64_t N, int64_t K, int qtype, int group_k, void* wq, q4fc_stream_t stream);
+
+/* Replaces offline_FC_dequant_Q4A (ops/op_fc.hpp:124-149).
+ * out: fp32 [Ng*32][Kg*group_k].  nibble_signed = 0 reproduces the reference
+ * (unsigned nibble for both block types). */
+int q4fc_dequant(const void* wq, int64_t Ng, int64_t Kg, int qtype, int group_k, int nibble_signed, float* out,
+                 q4fc_stream_t stream);
+
+/* Replaces FC_dynamic_quantize_x (ops/op_fc.hpp:221-272, with get_amax and
+ * quant_row_q8_0 of ops/utils.hpp:177-220).  x: fp32 [rows][K] with row
+ * stride ldx.  codes: int8 [rows][Kg*group_k]; scales, gsums: fp32
+ * [rows][Kg] (gsums may be NULL).  scale = 1 for Q4_1, 1/16 for Q4_0 as in
+ * ops/op_fc.hpp:315.  Codes, scales and group sums are bit-exact (the sums
+ * are accumulated sequentially like the reference's). */
+int q4fc_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int group_k, float scale, int8_t* codes,
+                 float* scales, float* gsums, q4fc_stream_t stream);
+
+/* Replaces fc_Q4A (ops/op_fc.hpp:286-426; old extension FC_evaluate_Q4A,
+ * ext/llama_ext.cpp:484-606): y[r][n] = quantized(x[r]) . W[n], r < rows,
+ * n < N.  x: fp32 [rows][K] (row stride ldx), y: fp32 [rows][N] (row stride
+ * ldy).  rows is the reference's B*M.  The activation quantization happens
+ * inside, as in the reference.
+ *   q4fc_fc_decode  rows <= 8: weight-streaming GEMV, HBM-bound.
+ *   q4fc_fc_prefill any rows:  int8 tensor-core GEMM.
+ *   q4fc_fc         picks one of the two.
+ * ws: workspace of at least q4fc_fc_workspace_bytes() bytes, 256-byte
+ * aligned, zeroed once with q4fc_fc_workspace_init() before its first use;
+ * the kernels leave it ready for the next call.  Calls that may overlap on
+ * the GPU need separate workspaces. */
+size_t q4fc_fc_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int group_k);
+int q4fc_fc_workspace_init(void* ws, size_t ws_bytes, q4fc_stream_t stream);
+int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                   int qtype, int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
+                   unsigned flags, q4fc_stream_t stream);
+int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                    int qtype, int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
+                    unsigned flags, q4fc_stream_t stream);
+int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg, int qtype,
+            int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
+            q4fc_stream_t stream);
+
+/* Reads and clears the device status word kept at the start of a workspace
+ * (host-synchronous: waits for `stream`).  Returns Q4FC_OK or Q4FC_EDEVICE. */
+int q4fc_fc_check_status(void* ws, q4fc_stream_t stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4FC_B200_H */

@@ -1,0 +1,87 @@
+"""ctypes binding of ``lib/libq4fc_b200.so`` (C-ABI in ``include/q4fc_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, a
+``RuntimeError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "lib", "libq4fc_b200.so")
+
+Q4_0, Q4_1 = 0, 1
+FLAG_NIBBLE_SIGNED = 1
+FLAG_PDL = 2
+
+# every symbol declared in include/q4fc_b200.h
+SYMBOLS = (
+    "q4fc_version", "q4fc_strerror", "q4fc_last_error", "q4fc_block_bytes", "q4fc_infer_variant",
+    "q4fc_pack", "q4fc_dequant", "q4fc_quant_x", "q4fc_fc_workspace_bytes", "q4fc_fc_workspace_init",
+    "q4fc_fc_decode", "q4fc_fc_prefill", "q4fc_fc", "q4fc_fc_check_status",
+)
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python llama.cl_b200/build.py` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback.")
+    L = C.CDLL(LIB_PATH)
+    i64, i32, u32, vp, sz, f32 = C.c_int64, C.c_int, C.c_uint, C.c_void_p, C.c_size_t, C.c_float
+    L.q4fc_version.restype = i32
+    L.q4fc_strerror.restype = C.c_char_p
+    L.q4fc_strerror.argtypes = [i32]
+    L.q4fc_last_error.restype = C.c_char_p
+    L.q4fc_block_bytes.argtypes = [i32, i32]
+    L.q4fc_infer_variant.argtypes = [i32, C.POINTER(i32), C.POINTER(i32)]
+    L.q4fc_pack.argtypes = [vp, i64, i64, i32, i32, vp, vp]
+    L.q4fc_dequant.argtypes = [vp, i64, i64, i32, i32, i32, vp, vp]
+    L.q4fc_quant_x.argtypes = [vp, i64, i64, i64, i32, f32, vp, vp, vp, vp]
+    L.q4fc_fc_workspace_bytes.restype = sz
+    L.q4fc_fc_workspace_bytes.argtypes = [i64, i64, i64, i32, i32]
+    L.q4fc_fc_workspace_init.argtypes = [vp, sz, vp]
+    fc_args = [vp, i64, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, vp, sz, u32, vp]
+    for name in ("q4fc_fc_decode", "q4fc_fc_prefill", "q4fc_fc"):
+        getattr(L, name).argtypes = fc_args
+    L.q4fc_fc_check_status.argtypes = [vp, vp]
+    _lib = L
+    return L
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        L = lib()
+        raise RuntimeError(
+            f"{what}: {L.q4fc_strerror(rc).decode()} ({rc}): {L.q4fc_last_error().decode()}")
+
+
+_VARIANTS = {576: (Q4_0, 32), 2112: (Q4_0, 128), 640: (Q4_1, 32), 2176: (Q4_1, 128)}
+
+
+def infer_variant(block_bytes: int) -> tuple[int, int]:
+    """(qtype, group_k) from the last dimension of a packed tensor."""
+    try:
+        return _VARIANTS[int(block_bytes)]
+    except KeyError:
+        raise RuntimeError(
+            f"assert weiq.size(2) == sizeof(q4_block) failed: block size {block_bytes} "
+            "is none of 576 / 640 / 2112 / 2176") from None
+
+
+def block_bytes(qtype: int, group_k: int) -> int:
+    return 16 * group_k + (128 if qtype == Q4_1 else 64)
+
+
+def parse_qtype(qtype) -> int:
+    if qtype in (Q4_0, "q4_0", "Q4_0"):
+        return Q4_0
+    if qtype in (Q4_1, "q4_1", "Q4_1"):
+        return Q4_1
+    raise RuntimeError(f"unknown qtype {qtype!r}: expected 'q4_0' or 'q4_1'")

@@ -1,0 +1,279 @@
+// extern "C" entry points declared in include/q4fc_b200.h: argument checks,
+// error text, dispatch to the kernel launchers.  No entry point allocates or
+// synchronizes (q4fc_fc_check_status excepted, which is documented as
+// host-synchronous).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace q4fc {
+
+namespace {
+thread_local char g_err[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
+    return Q4FC_ECUDA;
+}
+
+const DeviceInfo* device_info() {
+    static DeviceInfo info[64];
+    static bool ready[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        set_error("no current CUDA device");
+        return nullptr;
+    }
+    if (!ready[dev]) {
+        int sms = 0, smem = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+            cudaGetLastError();
+            set_error("cannot query device %d", dev);
+            return nullptr;
+        }
+        info[dev].sm_count = sms;
+        info[dev].max_smem_optin = smem;
+        ready[dev] = true;
+    }
+    return &info[dev];
+}
+
+namespace {
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int check_variant(int qtype, int G, const char* who) {
+    if (!valid_variant(qtype, G)) {
+        set_error("%s: unsupported block type (qtype=%d, group_k=%d); expected Q4_0/Q4_1 with group 32 or 128", who,
+                  qtype, G);
+        return Q4FC_EVARIANT;
+    }
+    return Q4FC_OK;
+}
+
+int check_fc_args(const char* who, const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng,
+                  int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy) {
+    if (int rc = check_variant(qtype, G, who)) return rc;
+    if (rows < 0 || K <= 0 || N < 0 || Ng < 0 || Kg <= 0) {
+        set_error("%s: negative or empty size (rows=%lld K=%lld N=%lld Ng=%lld Kg=%lld)", who, (long long)rows,
+                  (long long)K, (long long)N, (long long)Ng, (long long)Kg);
+        return Q4FC_EINVAL;
+    }
+    if ((K + G - 1) / G != Kg) {
+        set_error("%s: K=%lld does not match Kg=%lld groups of %d", who, (long long)K, (long long)Kg, G);
+        return Q4FC_EINVAL;
+    }
+    if (N > Ng * 32) {
+        set_error("%s: N=%lld exceeds the %lld columns of the packed tensor", who, (long long)N, (long long)(Ng * 32));
+        return Q4FC_EINVAL;
+    }
+    if (rows > 0 && N > 0) {
+        if (!x || !wq || !y) {
+            set_error("%s: null pointer", who);
+            return Q4FC_EINVAL;
+        }
+        if (ldx < K || ldy < N) {
+            set_error("%s: leading dimension smaller than the row (ldx=%lld K=%lld ldy=%lld N=%lld)", who,
+                      (long long)ldx, (long long)K, (long long)ldy, (long long)N);
+            return Q4FC_EINVAL;
+        }
+        if (!aligned(wq, 16) || !aligned(x, 4) || !aligned(y, 4)) {
+            set_error("%s: packed weights need 16-byte alignment, x and y 4-byte", who);
+            return Q4FC_EALIGN;
+        }
+    }
+    return Q4FC_OK;
+}
+
+}  // namespace
+}  // namespace q4fc
+
+using namespace q4fc;
+
+extern "C" {
+
+int q4fc_version(void) { return 100; }
+
+const char* q4fc_strerror(int code) {
+    switch (code) {
+        case Q4FC_OK: return "ok";
+        case Q4FC_EINVAL: return "invalid argument";
+        case Q4FC_EVARIANT: return "unsupported block variant";
+        case Q4FC_EALIGN: return "misaligned pointer or leading dimension";
+        case Q4FC_EWORKSPACE: return "workspace missing or too small";
+        case Q4FC_ECUDA: return "CUDA runtime error";
+        case Q4FC_EDEVICE: return "device-side wait ran out";
+        case Q4FC_ELIMIT: return "size beyond a supported maximum";
+        default: return "unknown error";
+    }
+}
+
+const char* q4fc_last_error(void) { return g_err; }
+
+int q4fc_block_bytes(int qtype, int group_k) { return valid_variant(qtype, group_k) ? block_bytes(qtype, group_k) : -1; }
+
+int q4fc_infer_variant(int bs, int* qtype, int* group_k) {
+    for (int q = 0; q < 2; q++)
+        for (int G : {32, 128})
+            if (block_bytes(q, G) == bs) {
+                if (qtype) *qtype = q;
+                if (group_k) *group_k = G;
+                return Q4FC_OK;
+            }
+    set_error("block size %d is none of 576 / 640 / 2112 / 2176", bs);
+    return Q4FC_EVARIANT;
+}
+
+int q4fc_pack(const float* w, int64_t N, int64_t K, int qtype, int group_k, void* wq, q4fc_stream_t stream) {
+    if (int rc = check_variant(qtype, group_k, "pack")) return rc;
+    if (N < 0 || K < 0) {
+        set_error("pack: negative size");
+        return Q4FC_EINVAL;
+    }
+    if (N == 0 || K == 0) return Q4FC_OK;
+    if (!w || !wq) {
+        set_error("pack: null pointer");
+        return Q4FC_EINVAL;
+    }
+    if (!aligned(wq, 16) || !aligned(w, 4)) {
+        set_error("pack: output needs 16-byte alignment, input 4-byte");
+        return Q4FC_EALIGN;
+    }
+    return launch_pack(w, N, K, qtype, group_k, static_cast<uint8_t*>(wq), static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_dequant(const void* wq, int64_t Ng, int64_t Kg, int qtype, int group_k, int nibble_signed, float* out,
+                 q4fc_stream_t stream) {
+    if (int rc = check_variant(qtype, group_k, "dequant")) return rc;
+    if (Ng < 0 || Kg < 0) {
+        set_error("dequant: negative size");
+        return Q4FC_EINVAL;
+    }
+    if (Ng == 0 || Kg == 0) return Q4FC_OK;
+    if (!wq || !out) {
+        set_error("dequant: null pointer");
+        return Q4FC_EINVAL;
+    }
+    if (!aligned(wq, 4) || !aligned(out, 16)) {
+        set_error("dequant: output needs 16-byte alignment, packed input 4-byte");
+        return Q4FC_EALIGN;
+    }
+    return launch_dequant(static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, nibble_signed, out,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int group_k, float scale, int8_t* codes,
+                 float* scales, float* gsums, q4fc_stream_t stream) {
+    if (group_k != 32 && group_k != 128) {
+        set_error("quant_x: group_k=%d, expected 32 or 128", group_k);
+        return Q4FC_EVARIANT;
+    }
+    if (rows < 0 || K < 0) {
+        set_error("quant_x: negative size");
+        return Q4FC_EINVAL;
+    }
+    if (rows == 0 || K == 0) return Q4FC_OK;
+    if (!x || !codes || !scales) {
+        set_error("quant_x: null pointer");
+        return Q4FC_EINVAL;
+    }
+    if (ldx < K) {
+        set_error("quant_x: ldx=%lld smaller than K=%lld", (long long)ldx, (long long)K);
+        return Q4FC_EINVAL;
+    }
+    if (!aligned(codes, 4) || !aligned(x, 4)) {
+        set_error("quant_x: codes and x need 4-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    return launch_quant_x(x, rows, K, ldx, group_k, scale, codes, scales, gsums, static_cast<cudaStream_t>(stream));
+}
+
+size_t q4fc_fc_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int group_k) {
+    if (!valid_variant(qtype, group_k) || rows < 0 || K < 0 || N < 0) return 0;
+    size_t need = decode_workspace_bytes(N);
+    if (rows > kMaxDecodeRows) {
+        size_t p = prefill_workspace_bytes(rows, K, N, qtype, group_k);
+        if (p > need) need = p;
+    }
+    return need;
+}
+
+int q4fc_fc_workspace_init(void* ws, size_t ws_bytes, q4fc_stream_t stream) {
+    if (!ws || ws_bytes < kWsStatusBytes) {
+        set_error("workspace_init: null or tiny workspace");
+        return Q4FC_EWORKSPACE;
+    }
+    if (!aligned(ws, 256)) {
+        set_error("workspace_init: workspace needs 256-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    Q4FC_CUDA_OK(cudaMemsetAsync(ws, 0, ws_bytes, static_cast<cudaStream_t>(stream)));
+    return Q4FC_OK;
+}
+
+int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                   int qtype, int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
+                   unsigned flags, q4fc_stream_t stream) {
+    if (int rc = check_fc_args("fc_decode", x, rows, K, ldx, wq, Ng, Kg, qtype, group_k, N, y, ldy)) return rc;
+    if (rows > kMaxDecodeRows) {
+        set_error("fc_decode: rows=%lld exceeds %d; use q4fc_fc or q4fc_fc_prefill", (long long)rows, kMaxDecodeRows);
+        return Q4FC_ELIMIT;
+    }
+    if (ws && !aligned(ws, 256)) {
+        set_error("fc_decode: workspace needs 256-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    return launch_fc_decode(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y, ldy,
+                            ws, ws_bytes, flags, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                    int qtype, int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
+                    unsigned flags, q4fc_stream_t stream) {
+    if (int rc = check_fc_args("fc_prefill", x, rows, K, ldx, wq, Ng, Kg, qtype, group_k, N, y, ldy)) return rc;
+    if (ws && !aligned(ws, 256)) {
+        set_error("fc_prefill: workspace needs 256-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    return launch_fc_prefill(x, rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y, ldy, ws,
+                             ws_bytes, flags, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg, int qtype,
+            int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
+            q4fc_stream_t stream) {
+    if (rows <= kMaxDecodeRows)
+        return q4fc_fc_decode(x, rows, K, ldx, wq, Ng, Kg, qtype, group_k, N, y, ldy, ws, ws_bytes, flags, stream);
+    return q4fc_fc_prefill(x, rows, K, ldx, wq, Ng, Kg, qtype, group_k, N, y, ldy, ws, ws_bytes, flags, stream);
+}
+
+int q4fc_fc_check_status(void* ws, q4fc_stream_t stream) {
+    if (!ws) {
+        set_error("check_status: null workspace");
+        return Q4FC_EWORKSPACE;
+    }
+    int status = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    Q4FC_CUDA_OK(cudaMemcpyAsync(&status, ws, sizeof(int), cudaMemcpyDeviceToHost, s));
+    Q4FC_CUDA_OK(cudaStreamSynchronize(s));
+    if (status != 0) {
+        Q4FC_CUDA_OK(cudaMemsetAsync(ws, 0, sizeof(int), s));
+        set_error("device status word = 0x%x (a bounded wait ran out)", status);
+        return Q4FC_EDEVICE;
+    }
+    return Q4FC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,90 @@
+// Shared definitions of the sm_100a quantized-FC kernels: the reference's
+// block layout (ops/op_fc.hpp:14-24, 64-71), error plumbing and small device
+// helpers.  One block = 32 columns x G k:
+//   bytes [0, 16*G)           G/8 rows of 128 B; a 32-bit word at row r,
+//                             column n holds k = 8r..8r+3 in the low nibbles
+//                             of its 4 bytes and k = 8r+4..8r+7 in the high
+//   bytes [16*G, 16*G+64)     32 fp16 scales wd
+//   bytes [16*G+64, +128)     32 fp16 minima wm (Q4_1 only)
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/q4fc_b200.h"
+
+namespace q4fc {
+
+constexpr int kGroupN = 32;  // columns per block (group_n, ops/op_fc.hpp:17)
+constexpr int kMaxDecodeRows = 8;
+
+__host__ __device__ constexpr int block_bytes(int qtype, int G) { return 16 * G + (qtype ? 128 : 64); }
+
+inline bool valid_variant(int qtype, int G) { return (qtype == 0 || qtype == 1) && (G == 32 || G == 128); }
+
+// thread-local detail text behind q4fc_last_error()
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define Q4FC_CUDA_OK(expr)                                     \
+    do {                                                       \
+        cudaError_t e__ = (expr);                              \
+        if (e__ != cudaSuccess) return q4fc::cuda_fail(e__, #expr); \
+    } while (0)
+
+struct DeviceInfo {
+    int sm_count;
+    int max_smem_optin;
+};
+// cached per device; returns nullptr (and sets the error text) on failure
+const DeviceInfo* device_info();
+
+// ---- workspace layout of the FC entry points ------------------------------
+// [0, 256)            status word (int) + padding
+// [256, 256+4*NgMax)  per-stripe arrival counters (int), zero between calls
+// then                CTA partials: [ctas][2][8][32] fp32
+constexpr size_t kWsStatusBytes = 256;
+
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// launchers implemented in the kernel translation units
+int launch_pack(const float* w, int64_t N, int64_t K, int qtype, int G, uint8_t* wq, cudaStream_t s);
+int launch_dequant(const uint8_t* wq, int64_t Ng, int64_t Kg, int qtype, int G, int nibble_signed, float* out,
+                   cudaStream_t s);
+int launch_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int G, float scale, int8_t* codes,
+                   float* scales, float* gsums, cudaStream_t s);
+size_t decode_workspace_bytes(int64_t N);
+int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
+                     int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
+                     cudaStream_t s);
+size_t prefill_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int G);
+int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
+                      int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
+                      unsigned flags, cudaStream_t s);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ uint16_t f2h_rn(float f) { return __half_as_ushort(__float2half_rn(f)); }
+
+// streaming 128-bit load: read-only path, no L1 allocation
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream_v2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// programmatic dependent launch: both are no-ops when the kernel was launched
+// without the programmatic-serialization attribute
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
+}  // namespace q4fc

@@ -1,0 +1,465 @@
+// Decode FC (rows <= 8): weight-streaming GEMV over the reference's packed
+// Q4_0 / Q4_1 tensor.  Replaces fc_Q4A (ops/op_fc.hpp:286-426) for small
+// B*M.  HBM-bound: every packed byte is read exactly once.
+//
+// Decomposition.  The packed tensor [Ng][Kg][BS] is one contiguous byte
+// stream; its Ng*Kg blocks are dealt out in memory order, an equal contiguous
+// run per CTA and, inside the CTA, an equal contiguous run per warp
+// ("stream-K": every SM streams the same number of bytes whatever N and K
+// are).  A run crosses stripe (32-column) boundaries freely; a warp keeps
+// fp32 accumulators for the stripe it is in and emits a "segment" when the
+// stripe changes.
+//
+// Inner product.  One lane loads 128 bits = 4 columns x 8 k of packed
+// nibbles straight from global memory (a warp covers 512 contiguous bytes, 4
+// block rows); `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are the two u8x4
+// operands for k..k+3 and k+4..k+7 (ops/op_fc.hpp:39-48).  They feed
+// mma.sync.m16n8k32 (u8 x s8 -> s32) with the 16-row side holding weight
+// columns and the 8-column side holding the activation rows, so the group dot
+// product is exact in int32 and costs the same for 1..8 rows.  The k order
+// inside the MMA is permuted consistently on both operands.  Loads for the
+// next step are issued before the current step is consumed; the registers
+// are the staging buffer (~70 KB in flight per SM).
+//
+// Scaling (ops/op_fc.hpp:381-412) after every K group:
+//   acc = fmaf(fp32(wd) * xs, (float)I, acc);  Q4_1: acc = fmaf(fp32(wm), gsum, acc)
+// Q4_0 follows the reference's reading of the stored nibble as UNSIGNED
+// (ops/op_fc.hpp:364-376); its x16 operand shift and 1/16 scale cancel exactly
+// and are not materialised.  The SIGNED instantiation sign-extends instead:
+// sum((nib ^ 8) * code) - 8 * sum(code).
+//
+// Activations.  Each CTA quantizes the rows itself (amax, codes, scale, group
+// sum: ops/op_fc.hpp:246-268 with the rounding rules of ops/utils.hpp:200-220)
+// into shared memory; codes and scales are bit-equal to the reference's, group
+// sums are tree-ordered.  Under programmatic dependent launch the first
+// weight loads are issued before the wait on the preceding kernel, since
+// weights never depend on it.
+//
+// Reduction.  Warp segments that do not cover a whole stripe are summed per
+// CTA in shared memory in warp order; stripes shared between CTAs go through
+// a workspace slot per CTA plus an arrival counter per stripe, and the last
+// CTA to arrive adds the slots in CTA order.  There is no spin-wait anywhere
+// and the result does not depend on timing.
+#include "common.cuh"
+
+namespace q4fc {
+namespace {
+
+constexpr int kDecWarps = 8;
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr uint32_t kNibMask = 0x0F0F0F0Fu;
+
+struct DecodeParams {
+    const float* x;
+    float* y;
+    const uint8_t* wq;
+    int* counters;
+    float* partials;
+    int64_t K, ldx, N, ldy;
+    int rows;
+    int Ng, Kg;
+    int T;            // Ng * Kg
+    int code_stride;  // bytes between code rows in shared memory
+    int x_vec_ok, y_vec_ok;
+};
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// CTA that owns block b under the split start(c) = floor(c*T/P)
+__device__ __forceinline__ int cta_of_block(int64_t b, int64_t T, int64_t P) { return (int)(((b + 1) * P + T - 1) / T - 1); }
+
+template <int G, int QTYPE, bool SIGNED>
+struct Dec {
+    static constexpr int BS = block_bytes(QTYPE, G);
+    static constexpr int SETS = G / 32;               // 4-row sets per block
+    static constexpr int NBLK = (G == 32) ? 4 : 1;    // blocks per pipeline step
+
+    struct Step {
+        uint4 q[NBLK][SETS];
+        uint2 wd[NBLK];
+        uint2 wm[NBLK];
+    };
+
+    // lane (g,t): rows 4j+t of each set, 16-byte chunk g of the 128-byte row
+    static __device__ __forceinline__ void load_step(Step& s, const uint8_t* wq, int b, int b_end, int g, int t) {
+#pragma unroll
+        for (int i = 0; i < NBLK; i++) {
+            if (b + i < b_end) {
+                const uint8_t* blk = wq + (int64_t)(b + i) * BS;
+#pragma unroll
+                for (int j = 0; j < SETS; j++) s.q[i][j] = ldg_stream_v4(blk + (4 * j + t) * 128 + g * 16);
+                s.wd[i] = ldg_stream_v2(blk + 16 * G + g * 8);
+                if (QTYPE == 1) s.wm[i] = ldg_stream_v2(blk + 16 * G + 64 + g * 8);
+            }
+        }
+    }
+};
+
+template <int G, int QTYPE, bool SIGNED>
+__global__ void __launch_bounds__(kDecThreads, 2) fc_decode_kernel(const DecodeParams p) {
+    using D = Dec<G, QTYPE, SIGNED>;
+    constexpr int BS = D::BS;
+    constexpr int SETS = D::SETS;
+    constexpr int NBLK = D::NBLK;
+
+    extern __shared__ __align__(16) uint8_t smem[];
+    // layout: wpart [W][2][8][32] f32 | seg_nb [W][2] int | sc [Kg][8][2] f32 | codes [rows][code_stride]
+    float* wpart = reinterpret_cast<float*>(smem);
+    int* seg_nb = reinterpret_cast<int*>(smem + kDecWarps * 2 * 8 * 32 * 4);
+    float* sc = reinterpret_cast<float*>(smem + kDecWarps * 2 * 8 * 32 * 4 + 64);
+    uint8_t* codes = reinterpret_cast<uint8_t*>(sc + (int64_t)p.Kg * 16);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t T = p.T, P = gridDim.x;
+    const int cb0 = (int)(((int64_t)blockIdx.x * T) / P);
+    const int cb1 = (int)(((int64_t)(blockIdx.x + 1) * T) / P);
+    const int Lc = cb1 - cb0;
+    const int wb0 = cb0 + (int)(((int64_t)warp * Lc) / kDecWarps);
+    const int wb1 = cb0 + (int)(((int64_t)(warp + 1) * Lc) / kDecWarps);
+
+    pdl_launch_dependents();
+
+    // weights do not depend on the preceding kernel: start streaming them now
+    typename D::Step cur, nxt;
+    D::load_step(cur, p.wq, wb0, wb1, g, t);
+
+    if (lane < 2) seg_nb[warp * 2 + lane] = -1;
+
+    pdl_wait_prior_grid();
+
+    // ---- quantize the activation rows into shared memory -------------------
+    {
+        constexpr int SEG = G / 4;    // lanes per group
+        constexpr int GPC = 128 / G;  // groups per 128-k chunk
+        const int64_t Kp = (int64_t)p.Kg * G;
+        const int chunks = (int)((Kp + 127) / 128);
+        for (int u = warp; u < p.rows * chunks; u += kDecWarps) {
+            const int row = u / chunks, c = u % chunks;
+            const int64_t k = (int64_t)c * 128 + lane * 4;
+            const float* src = p.x + row * p.ldx + k;
+            float v[4];
+            if (p.x_vec_ok && k + 4 <= p.K) {
+                float4 a = __ldcg(reinterpret_cast<const float4*>(src));
+                v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) v[j] = (k + j < p.K) ? __ldcg(src + j) : 0.0f;
+            }
+            const int kb = c * GPC + lane / SEG;
+            const bool exists = kb < p.Kg;
+            const int len = exists ? (int)min((int64_t)G, p.K - (int64_t)kb * G) : 0;
+            const int body = (len / 8) * 8;
+            const int e0 = (lane % SEG) * 4;
+            float amax = 0.0f, fsum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (e0 + j < len) {
+                    amax = fmaxf(amax, fabsf(v[j]));
+                    fsum += v[j];
+                }
+#pragma unroll
+            for (int off = SEG / 2; off > 0; off >>= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, SEG));
+                fsum += __shfl_xor_sync(0xffffffffu, fsum, off, SEG);
+            }
+            const float d = __fdiv_rn(amax, 127.0f);
+            const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+            uint32_t packed = 0;
+            int isum = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int e = e0 + j;
+                int q = 0;
+                if (e < len) {
+                    const float tq = __fmul_rn(v[j], id);
+                    if (e < body) {
+                        q = __float2int_rn(tq);
+                    } else {
+                        const float h = __int_as_float((__float_as_int(tq) & 0x80000000) | 0x3F000000);
+                        q = __float2int_rz(__fadd_rz(tq, h));
+                    }
+                    q = min(127, max(-128, q));
+                }
+                isum += q;
+                packed |= (uint32_t)(q & 0xFF) << (8 * j);
+            }
+            if (SIGNED) {
+#pragma unroll
+                for (int off = SEG / 2; off > 0; off >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, off, SEG);
+            }
+            if (exists) {
+                *reinterpret_cast<uint32_t*>(codes + (int64_t)row * p.code_stride + k) = packed;
+                if (lane % SEG == 0) {
+                    // reference: x_scales = d * scale with scale = 1/16 for Q4_0, cancelled by its
+                    // x16 nibble shift; both are exact powers of two and are left out here
+                    sc[kb * 16 + row * 2 + 0] = d;
+                    sc[kb * 16 + row * 2 + 1] = SIGNED ? __int_as_float(8 * isum) : fsum;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- stream this warp's run of blocks ------------------------------------
+    float acc[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; i++) acc[i][0] = acc[i][1] = 0.0f;
+    int nslot = 0;
+    int b = wb0;
+    int nb = (wb0 < wb1) ? wb0 / p.Kg : 0;
+    int kb = (wb0 < wb1) ? wb0 % p.Kg : 0;
+    int seg_kb0 = kb;
+    const uint8_t* my_codes = codes + (int64_t)g * p.code_stride + 8 * t;
+    const bool row_live = g < p.rows;
+
+    auto emit = [&](int stripe, int kfirst, int kend) {
+        const int64_t n0 = (int64_t)stripe * 32 + g * 4;
+        if (kfirst == 0 && kend == p.Kg) {
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++) {
+                const int m = 2 * t + mi;
+                if (m < p.rows) {
+                    float* dst = p.y + m * p.ldy + n0;
+                    if (p.y_vec_ok && n0 + 4 <= p.N) {
+                        *reinterpret_cast<float4*>(dst) = make_float4(acc[0][mi], acc[1][mi], acc[2][mi], acc[3][mi]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            if (n0 + i < p.N) dst[i] = acc[i][mi];
+                    }
+                }
+            }
+        } else {
+            float* slot = wpart + (warp * 2 + nslot) * 256;
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++)
+                *reinterpret_cast<float4*>(slot + (2 * t + mi) * 32 + g * 4) =
+                    make_float4(acc[0][mi], acc[1][mi], acc[2][mi], acc[3][mi]);
+            if (lane == 0) seg_nb[warp * 2 + nslot] = stripe;
+            nslot++;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[i][0] = acc[i][1] = 0.0f;
+    };
+
+    auto process = [&](const typename D::Step& st) {
+    #pragma unroll
+        for (int i = 0; i < NBLK; i++) {
+            if (b + i < wb1) {
+                int ia[4] = {0, 0, 0, 0}, ib[4] = {0, 0, 0, 0};
+    #pragma unroll
+                for (int j = 0; j < SETS; j++) {
+                    uint2 xb = make_uint2(0u, 0u);
+                    if (row_live) xb = *reinterpret_cast<const uint2*>(my_codes + (int64_t)kb * G + 32 * j);
+                    const uint4 q = st.q[i][j];
+                    uint32_t l0 = q.x & kNibMask, l1 = q.y & kNibMask, l2 = q.z & kNibMask, l3 = q.w & kNibMask;
+                    uint32_t h0 = (q.x >> 4) & kNibMask, h1 = (q.y >> 4) & kNibMask, h2 = (q.z >> 4) & kNibMask,
+                             h3 = (q.w >> 4) & kNibMask;
+                    if (SIGNED) {
+                        l0 ^= 0x08080808u, l1 ^= 0x08080808u, l2 ^= 0x08080808u, l3 ^= 0x08080808u;
+                        h0 ^= 0x08080808u, h1 ^= 0x08080808u, h2 ^= 0x08080808u, h3 ^= 0x08080808u;
+                    }
+                    mma_u8s8(ia, l0, l1, h0, h1, xb.x, xb.y);
+                    mma_u8s8(ib, l2, l3, h2, h3, xb.x, xb.y);
+                }
+                // per-group scaling; lane holds columns 4g..4g+3 for rows 2t, 2t+1
+                const float4 s4 = *reinterpret_cast<const float4*>(sc + kb * 16 + t * 4);  // xs0, gs0, xs1, gs1
+                const float2 wd01 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].x));
+                const float2 wd23 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].y));
+                const float wdf[4] = {wd01.x, wd01.y, wd23.x, wd23.y};
+                const int iv[4][2] = {{ia[0], ia[1]}, {ia[2], ia[3]}, {ib[0], ib[1]}, {ib[2], ib[3]}};
+                const float xs[2] = {s4.x, s4.z};
+                const float gs[2] = {s4.y, s4.w};
+                float wmf[4] = {0.f, 0.f, 0.f, 0.f};
+                if (QTYPE == 1) {
+                    const float2 wm01 = __half22float2(*reinterpret_cast<const __half2*>(&st.wm[i].x));
+                    const float2 wm23 = __half22float2(*reinterpret_cast<const __half2*>(&st.wm[i].y));
+                    wmf[0] = wm01.x, wmf[1] = wm01.y, wmf[2] = wm23.x, wmf[3] = wm23.y;
+                }
+    #pragma unroll
+                for (int c = 0; c < 4; c++) {
+    #pragma unroll
+                    for (int mi = 0; mi < 2; mi++) {
+                        int I = iv[c][mi];
+                        if (SIGNED) I -= __float_as_int(gs[mi]);
+                        acc[c][mi] = fmaf(__fmul_rn(wdf[c], xs[mi]), (float)I, acc[c][mi]);
+                        if (QTYPE == 1) acc[c][mi] = fmaf(wmf[c], gs[mi], acc[c][mi]);
+                    }
+                }
+                // advance; close the segment at a stripe boundary
+                kb++;
+                if (kb == p.Kg) {
+                    emit(nb, seg_kb0, kb);
+                    kb = 0;
+                    seg_kb0 = 0;
+                    nb++;
+                }
+            }
+        }
+    };
+
+    // two register sets take turns as the staging buffer for the loads in flight
+    while (b < wb1) {
+        D::load_step(nxt, p.wq, b + NBLK, wb1, g, t);
+        process(cur);
+        b += NBLK;
+        if (b >= wb1) break;
+        D::load_step(cur, p.wq, b + NBLK, wb1, g, t);
+        process(nxt);
+        b += NBLK;
+    }
+    if (kb != seg_kb0) emit(nb, seg_kb0, kb);  // run ended inside a stripe
+    __syncthreads();
+
+    // ---- combine warp segments per stripe, then across CTAs ------------------
+    if (Lc <= 0) return;
+    const int nbF = cb0 / p.Kg, nbL = (cb1 - 1) / p.Kg;
+    for (int s = nbF + warp; s <= nbL; s += kDecWarps) {
+        float sum[kMaxDecodeRows];
+#pragma unroll
+        for (int m = 0; m < kMaxDecodeRows; m++) sum[m] = 0.0f;
+        bool found = false;
+        for (int i = 0; i < kDecWarps * 2; i++) {
+            if (seg_nb[i] == s) {
+                found = true;
+#pragma unroll
+                for (int m = 0; m < kMaxDecodeRows; m++)
+                    if (m < p.rows) sum[m] += wpart[i * 256 + m * 32 + lane];
+            }
+        }
+        if (!found) continue;  // every segment of this stripe was complete and already stored
+        const int64_t n = (int64_t)s * 32 + lane;
+        const bool whole = ((int64_t)s * p.Kg >= cb0) && ((int64_t)(s + 1) * p.Kg <= cb1);
+        if (whole) {
+#pragma unroll
+            for (int m = 0; m < kMaxDecodeRows; m++)
+                if (m < p.rows && n < p.N) p.y[m * p.ldy + n] = sum[m];
+            continue;
+        }
+        const int which = (s == nbF) ? 0 : 1;
+        float* slot = p.partials + ((int64_t)blockIdx.x * 2 + which) * 256;
+#pragma unroll
+        for (int m = 0; m < kMaxDecodeRows; m++)
+            if (m < p.rows) __stcg(slot + m * 32 + lane, sum[m]);
+        __threadfence();
+        __syncwarp();
+        const int cF = cta_of_block((int64_t)s * p.Kg, T, P);
+        const int cL = cta_of_block((int64_t)(s + 1) * p.Kg - 1, T, P);
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(p.counters + s, 1) + 1 == cL - cF + 1);
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) continue;
+        __threadfence();
+#pragma unroll
+        for (int m = 0; m < kMaxDecodeRows; m++) sum[m] = 0.0f;
+        for (int c = cF; c <= cL; c++) {
+            const int c_first_stripe = (int)((((int64_t)c * T) / P) / p.Kg);
+            const float* src = p.partials + ((int64_t)c * 2 + (c_first_stripe == s ? 0 : 1)) * 256;
+#pragma unroll
+            for (int m = 0; m < kMaxDecodeRows; m++)
+                if (m < p.rows) sum[m] += __ldcg(src + m * 32 + lane);
+        }
+#pragma unroll
+        for (int m = 0; m < kMaxDecodeRows; m++)
+            if (m < p.rows && n < p.N) p.y[m * p.ldy + n] = sum[m];
+        if (lane == 0) p.counters[s] = 0;  // ready for the next call
+    }
+}
+
+struct KernelEntry {
+    const void* fn;
+    bool attr_done[16];
+};
+
+template <int G, int QTYPE, bool SIGNED>
+int launch_variant(const DecodeParams& p, size_t smem, int grid, unsigned flags, cudaStream_t s) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    Q4FC_CUDA_OK(cudaGetDevice(&dev));
+    auto* fn = fc_decode_kernel<G, QTYPE, SIGNED>;
+    if (dev < 64 && !attr_done[dev]) {
+        const DeviceInfo* di = device_info();
+        if (!di) return Q4FC_ECUDA;
+        Q4FC_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin));
+        attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    int nattr = 0;
+    if (flags & Q4FC_FLAG_PDL) {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        nattr++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = nattr;
+    Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, fn, p));
+    return Q4FC_OK;
+}
+
+constexpr int kCtasPerSm = 2;
+
+}  // namespace
+
+size_t decode_workspace_bytes(int64_t N) {
+    const DeviceInfo* di = device_info();
+    const int sms = di ? di->sm_count : 256;
+    const int64_t Ng = (N + 31) / 32;
+    return kWsStatusBytes + align_up((size_t)Ng * 4, 256) + (size_t)sms * kCtasPerSm * 2 * 256 * sizeof(float);
+}
+
+int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
+                     int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
+                     cudaStream_t s) {
+    if (rows == 0 || N == 0) return Q4FC_OK;
+    const DeviceInfo* di = device_info();
+    if (!di) return Q4FC_ECUDA;
+    if (Ng * Kg >= 0x7fffffffLL) {
+        set_error("fc_decode: %lld blocks exceed the 2^31 limit", (long long)(Ng * Kg));
+        return Q4FC_ELIMIT;
+    }
+    if (ws == nullptr || ws_bytes < decode_workspace_bytes(N)) {
+        set_error("fc_decode: workspace of %zu bytes given, %zu needed", ws_bytes, decode_workspace_bytes(N));
+        return Q4FC_EWORKSPACE;
+    }
+    DecodeParams p;
+    p.x = x, p.y = y, p.wq = wq;
+    p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kWsStatusBytes);
+    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kWsStatusBytes + align_up((size_t)Ng * 4, 256));
+    p.K = K, p.ldx = ldx, p.N = N, p.ldy = ldy;
+    p.rows = rows, p.Ng = (int)Ng, p.Kg = (int)Kg, p.T = (int)(Ng * Kg);
+    const int64_t Kp = Kg * G;
+    // code rows 32 bytes apart modulo 128 keep the 8-byte operand loads of a half warp on distinct banks
+    int64_t stride = (Kp + 127) / 128 * 128 + 32;
+    p.code_stride = (int)stride;
+    p.x_vec_ok = (K % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    p.y_vec_ok = (ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    const size_t smem = (size_t)kDecWarps * 2 * 8 * 32 * 4 + 64 + (size_t)Kg * 64 + (size_t)rows * stride;
+    if (smem > (size_t)di->max_smem_optin) {
+        set_error("fc_decode: rows=%d K=%lld needs %zu bytes of shared memory (limit %d)", rows, (long long)K, smem,
+                  di->max_smem_optin);
+        return Q4FC_ELIMIT;
+    }
+    int grid = di->sm_count * kCtasPerSm;
+    if (grid > p.T) grid = p.T;
+    const bool sgn = (flags & Q4FC_FLAG_NIBBLE_SIGNED) && qtype == 0;
+    if (qtype == 1 && G == 32) return launch_variant<32, 1, false>(p, smem, grid, flags, s);
+    if (qtype == 1 && G == 128) return launch_variant<128, 1, false>(p, smem, grid, flags, s);
+    if (qtype == 0 && G == 32 && !sgn) return launch_variant<32, 0, false>(p, smem, grid, flags, s);
+    if (qtype == 0 && G == 128 && !sgn) return launch_variant<128, 0, false>(p, smem, grid, flags, s);
+    if (qtype == 0 && G == 32) return launch_variant<32, 0, true>(p, smem, grid, flags, s);
+    return launch_variant<128, 0, true>(p, smem, grid, flags, s);
+}
+
+}  // namespace q4fc

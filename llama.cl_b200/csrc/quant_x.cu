@@ -1,0 +1,135 @@
+// Stand-alone Q8 activation quantizer.
+//
+// Replaces FC_dynamic_quantize_x (ops/op_fc.hpp:221-272) with get_amax and
+// quant_row_q8_0 (ops/utils.hpp:177-220): per row and K group
+//   amax = max|x|, d = amax/127, id = 1/d (0 when d == 0),
+//   scales = d * scale, codes = sat_s8(round(x * id)), gsums = sum of raw x.
+// Rounding follows the reference exactly: the first floor(len/8)*8 elements
+// of a group round half to even (its 8-wide AVX2 body), the remaining
+// len % 8 elements round half away from zero (its scalar tail); padding codes
+// are 0.  The group sum is accumulated sequentially in k order so that it is
+// bit-equal to the reference's loop (ops/op_fc.hpp:262-268).
+//
+// One warp owns 128 consecutive k of one row: a 512-byte coalesced read, four
+// values per lane.  The absolute maximum is a segmented butterfly over the
+// G/4 lanes of a group.  The raw values are parked in shared memory so that
+// one lane per group can walk them in order for the sequential sum; many
+// resident warps hide that serial chain.  The decode FC kernel has its own
+// fused copy of this arithmetic (tree-ordered sums); this kernel serves the
+// prefill path and callers that want the quantized activations themselves.
+#include "common.cuh"
+
+namespace q4fc {
+namespace {
+
+constexpr int kQxWarps = 8;
+
+__device__ __forceinline__ int sat8(int v) { return min(127, max(-128, v)); }
+
+template <int G>
+__global__ void __launch_bounds__(kQxWarps * 32) quant_x_kernel(const float* __restrict__ x, int64_t rows, int64_t K,
+                                                                int64_t ldx, int64_t Kg, float scale, int vec_ok,
+                                                                int8_t* __restrict__ codes, float* __restrict__ scales,
+                                                                float* __restrict__ gsums) {
+    constexpr int SEG = G / 4;     // lanes per group
+    constexpr int GPC = 128 / G;   // groups per 128-k chunk
+    constexpr int PADG = G + 1;    // padded group pitch in shared memory
+    __shared__ float raw[kQxWarps][GPC * PADG + 3];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t chunks = (Kg * G + 127) / 128;
+    const int64_t unit = (int64_t)blockIdx.x * kQxWarps + warp;
+    if (unit >= rows * chunks) return;
+    const int64_t row = unit / chunks;
+    const int64_t c = unit % chunks;
+    const int64_t k = c * 128 + lane * 4;
+    const float* src = x + row * ldx + k;
+
+    float v[4];
+    if (vec_ok && k + 4 <= K) {
+        float4 a = __ldg(reinterpret_cast<const float4*>(src));
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = (k + j < K) ? __ldg(src + j) : 0.0f;
+    }
+
+    const int g_l = lane / SEG;              // group inside the chunk
+    const int64_t kb = c * GPC + g_l;        // group index in the row
+    const bool group_exists = kb < Kg;
+    const int len = group_exists ? (int)min((int64_t)G, K - kb * G) : 0;
+    const int body = (len / 8) * 8;
+    const int e0 = (lane % SEG) * 4;         // element index of v[0] inside the group
+
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        if (e0 + j < len) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int off = SEG / 2; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, SEG));
+
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int e = e0 + j;
+        int q = 0;
+        if (e < len) {
+            const float t = __fmul_rn(v[j], id);
+            if (e < body) {
+                q = sat8(__float2int_rn(t));  // nearest even, as _mm256_round_ps + packs
+            } else {
+                const float h = __int_as_float((__float_as_int(t) & 0x80000000) | 0x3F000000);
+                q = sat8(__float2int_rz(__fadd_rz(t, h)));  // std::round: half away
+            }
+        }
+        packed |= (uint32_t)(q & 0xFF) << (8 * j);
+    }
+    if (group_exists) {
+        *reinterpret_cast<uint32_t*>(codes + row * (Kg * G) + k) = packed;
+        if (lane % SEG == 0) scales[row * Kg + kb] = __fmul_rn(d, scale);
+    }
+
+    if (gsums != nullptr) {
+        float* mine = raw[warp];
+#pragma unroll
+        for (int j = 0; j < 4; j++) mine[g_l * PADG + e0 + j] = v[j];
+        __syncwarp();
+        if (lane < GPC) {
+            const int64_t kb2 = c * GPC + lane;
+            if (kb2 < Kg) {
+                const int len2 = (int)min((int64_t)G, K - kb2 * G);
+                float s = 0.0f;
+                for (int i = 0; i < len2; i++) s = __fadd_rn(s, mine[lane * PADG + i]);
+                gsums[row * Kg + kb2] = s;
+            }
+        }
+    }
+}
+
+}  // namespace
+
+int launch_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int G, float scale, int8_t* codes,
+                   float* scales, float* gsums, cudaStream_t s) {
+    const int64_t Kg = (K + G - 1) / G;
+    if (rows == 0 || Kg == 0) return Q4FC_OK;
+    const int64_t chunks = (Kg * G + 127) / 128;
+    const int64_t grid = (rows * chunks + kQxWarps - 1) / kQxWarps;
+    if (grid > 0x7fffffffLL) {
+        set_error("quant_x: %lld x %lld exceeds the grid limit", (long long)rows, (long long)K);
+        return Q4FC_ELIMIT;
+    }
+    const int vec_ok = (K % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    if (G == 32)
+        quant_x_kernel<32><<<(unsigned)grid, kQxWarps * 32, 0, s>>>(x, rows, K, ldx, Kg, scale, vec_ok, codes, scales,
+                                                                    gsums);
+    else
+        quant_x_kernel<128><<<(unsigned)grid, kQxWarps * 32, 0, s>>>(x, rows, K, ldx, Kg, scale, vec_ok, codes,
+                                                                     scales, gsums);
+    Q4FC_CUDA_OK(cudaGetLastError());
+    return Q4FC_OK;
+}
+
+}  // namespace q4fc

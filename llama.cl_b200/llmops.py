@@ -1,0 +1,177 @@
+"""GPU drop-in for the FC ops of the reference's ``llmops`` module.
+
+Same names, positional arguments and result shapes as the pybind11 functions
+registered in ``ops/main.cpp:158-160`` of usstq/llama.cl, on torch CUDA
+tensors instead of ``llmops.tensor``:
+
+    offline_FC_quant_Q4A(wei)                  ops/op_fc.hpp:151
+    offline_FC_dequant_Q4A(weiq)               ops/op_fc.hpp:124
+    fc_Q4A(input, wei_quantized, N)            ops/op_fc.hpp:286
+
+The reference fixes the block type at compile time (``ops/op_fc.hpp:109``);
+here it is the keyword ``qtype`` / ``group_k`` of the packer (defaults: the
+reference's stock ``q4_1`` / 32) and is recovered from the packed tensor's
+last dimension everywhere else.  Errors surface as ``RuntimeError`` like the
+reference's ``ASSERT`` (``ops/tensor.hpp:20-36``).  Everything runs on the
+CUDA library; there is no CPU path.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, Q4_0, Q4_1
+
+__all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
+           "fc_workspace", "Workspace"]
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str, dtype: torch.dtype, rank: int) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name}: expected a torch.Tensor, got {type(t).__name__}")
+    if t.dtype != dtype or t.dim() != rank:
+        # mirrors ASSERT(x.is<T>(rank)) of the reference
+        raise RuntimeError(f"assert {name}.is<{str(dtype).replace('torch.', '')}>({rank}) failed: "
+                           f"got dtype {t.dtype}, rank {t.dim()}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name}: tensor must live on a CUDA device (there is no CPU path)")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name}: tensor must be dense row-major (contiguous)")
+
+
+class Workspace:
+    """Scratch for the FC kernels: status word, stripe counters, CTA partials.
+
+    Zeroed once at creation; the kernels leave it clean.  One workspace serves
+    any number of calls that are ordered on one stream."""
+
+    def __init__(self, nbytes: int, device: torch.device) -> None:
+        self.buf = torch.zeros(max(int(nbytes), 4096), dtype=torch.uint8, device=device)
+        self.nbytes = self.buf.numel()
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.data_ptr()
+
+    def check(self) -> None:
+        """Host-synchronous read of the device status word."""
+        with torch.cuda.device(self.buf.device):
+            _cabi.check(_cabi.lib().q4fc_fc_check_status(self.ptr, _stream_ptr(self.buf.device)), "fc status")
+
+
+_workspaces: dict = {}
+
+
+def fc_workspace(rows: int, K: int, N: int, qtype: int, group_k: int, device: torch.device) -> Workspace:
+    """Cached workspace for (device, current stream), grown on demand."""
+    with torch.cuda.device(device):
+        need = int(_cabi.lib().q4fc_fc_workspace_bytes(rows, K, N, qtype, group_k))
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.nbytes < need:
+        ws = Workspace(need, device)
+        _workspaces[key] = ws
+    return ws
+
+
+def offline_FC_quant_Q4A(wei: torch.Tensor, *, qtype="q4_1", group_k: int = 32,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 ``[N, K]`` -> int8 ``[ceil(N/32), ceil(K/group_k), block_bytes]`` (ops/op_fc.hpp:151-219)."""
+    q = _cabi.parse_qtype(qtype)
+    _require_cuda(wei, "wei", torch.float32, 2)
+    N, K = wei.shape
+    bs = _cabi.lib().q4fc_block_bytes(q, group_k)
+    if bs < 0:
+        raise RuntimeError(f"unsupported block type: qtype={qtype!r}, group_k={group_k}")
+    Ng, Kg = (N + 31) // 32, (K + group_k - 1) // group_k
+    if out is None:
+        out = torch.empty((Ng, Kg, bs), dtype=torch.int8, device=wei.device)
+    else:
+        _require_cuda(out, "out", torch.int8, 3)
+        if tuple(out.shape) != (Ng, Kg, bs):
+            raise RuntimeError(f"out: expected shape {(Ng, Kg, bs)}, got {tuple(out.shape)}")
+    with torch.cuda.device(wei.device):
+        _cabi.check(_cabi.lib().q4fc_pack(wei.data_ptr(), N, K, q, group_k, out.data_ptr(), _stream_ptr(wei.device)),
+                    "offline_FC_quant_Q4A")
+    return out
+
+
+def offline_FC_dequant_Q4A(weiq: torch.Tensor, *, nibble_signed: bool = False) -> torch.Tensor:
+    """packed -> fp32 ``[Ng*32, Kg*group_k]`` (ops/op_fc.hpp:124-149).
+
+    ``nibble_signed=False`` reads the nibble unsigned for Q4_0 too, as the
+    reference does (ops/op_fc.hpp:95-106)."""
+    _require_cuda(weiq, "weiq", torch.int8, 3)
+    Ng, Kg, bs = weiq.shape
+    q, G = _cabi.infer_variant(bs)
+    out = torch.empty((Ng * 32, Kg * G), dtype=torch.float32, device=weiq.device)
+    with torch.cuda.device(weiq.device):
+        _cabi.check(_cabi.lib().q4fc_dequant(weiq.data_ptr(), Ng, Kg, q, G, int(nibble_signed), out.data_ptr(),
+                                             _stream_ptr(weiq.device)), "offline_FC_dequant_Q4A")
+    return out
+
+
+def FC_dynamic_quantize_x(input: torch.Tensor, group_k: int, scale: float = 1.0):
+    """Q8 activation quantizer (ops/op_fc.hpp:221-272; not exported to Python by the reference).
+
+    fp32 ``[..., K]`` -> (codes int8 ``[..., Kg*group_k]``, scales fp32 ``[..., Kg]``, group sums fp32 ``[..., Kg]``)."""
+    if not isinstance(input, torch.Tensor) or input.dtype != torch.float32 or input.dim() < 1:
+        raise RuntimeError("input: expected an fp32 tensor of rank >= 1")
+    if not input.is_cuda or not input.is_contiguous():
+        raise RuntimeError("input: must be a contiguous CUDA tensor")
+    K = input.shape[-1]
+    rows = input.numel() // K if K else 0
+    Kg = (K + group_k - 1) // group_k
+    lead = tuple(input.shape[:-1])
+    codes = torch.empty(lead + (Kg * group_k,), dtype=torch.int8, device=input.device)
+    scales = torch.empty(lead + (Kg,), dtype=torch.float32, device=input.device)
+    gsums = torch.empty(lead + (Kg,), dtype=torch.float32, device=input.device)
+    with torch.cuda.device(input.device):
+        _cabi.check(_cabi.lib().q4fc_quant_x(input.data_ptr(), rows, K, K, group_k, float(scale), codes.data_ptr(),
+                                             scales.data_ptr(), gsums.data_ptr(), _stream_ptr(input.device)),
+                    "FC_dynamic_quantize_x")
+    return codes, scales, gsums
+
+
+def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_signed: bool = False,
+           out: torch.Tensor | None = None, workspace: Workspace | None = None, pdl: bool = False,
+           path: str = "auto") -> torch.Tensor:
+    """``y[b, m, :N] = quantized(input[b, m]) . W`` (ops/op_fc.hpp:286-426).
+
+    input fp32 ``[B, M, K]``, wei_quantized int8 ``[Ng, Kg, block_bytes]`` ->
+    fp32 ``[B, M, N]``.  ``path``: "auto" (decode kernel for B*M <= 8, else
+    the prefill kernel), "decode" or "prefill"."""
+    _require_cuda(input, "input", torch.float32, 3)
+    _require_cuda(wei_quantized, "wei_quantized", torch.int8, 3)
+    if wei_quantized.device != input.device:
+        raise RuntimeError("input and wei_quantized live on different devices")
+    B, M, K = input.shape
+    Ng, Kg, bs = wei_quantized.shape
+    q, G = _cabi.infer_variant(bs)
+    N = int(N)
+    rows = B * M
+    if out is None:
+        out = torch.empty((B, M, N), dtype=torch.float32, device=input.device)
+    else:
+        _require_cuda(out, "out", torch.float32, 3)
+        if tuple(out.shape) != (B, M, N):
+            raise RuntimeError(f"out: expected shape {(B, M, N)}, got {tuple(out.shape)}")
+    if workspace is None:
+        workspace = fc_workspace(rows, K, N, q, G, input.device)
+    flags = (FLAG_NIBBLE_SIGNED if nibble_signed else 0) | (FLAG_PDL if pdl else 0)
+    L = _cabi.lib()
+    fn = {"auto": L.q4fc_fc, "decode": L.q4fc_fc_decode, "prefill": L.q4fc_fc_prefill}[path]
+    with torch.cuda.device(input.device):
+        _cabi.check(fn(input.data_ptr(), rows, K, K, wei_quantized.data_ptr(), Ng, Kg, q, G, N, out.data_ptr(), N,
+                       workspace.ptr, workspace.nbytes, flags, _stream_ptr(input.device)), "fc_Q4A")
+    return out
+
+
+def fc_Q4A2(input, wei_quantized, N):
+    """Bound by the reference (ops/main.cpp:161) but its body is compiled out (ops/op_fc.hpp:428-623)."""
+    raise RuntimeError("fc_Q4A2 has no implementation in the reference; use fc_Q4A")

@@ -1,0 +1,327 @@
+"""CUDA path vs the CPU oracle and the reference's golden vectors, through the C-ABI.
+
+Bars: bit-exact for packed weights, dequantized weights, Q8 codes, scales and
+group sums; FC outputs within rtol 1e-3 / atol 1e-4 of the reference's CPU FC
+(the tolerance stated for this path), in practice ~1e-6.
+"""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+VARIANTS = [(0, 32), (0, 128), (1, 32), (1, 128)]
+QNAME = {0: "q4_0", 1: "q4_1"}
+RTOL, ATOL = 1e-3, 1e-4
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def pkg(lib_built):
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    import llama_cl_b200
+
+    return llama_cl_b200
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def close(y, ref):
+    return np.allclose(y, ref, rtol=RTOL, atol=ATOL)
+
+
+# ---------------------------------------------------------------- packer ----
+@pytest.mark.parametrize("qtype,G", VARIANTS)
+def test_pack_golden(pkg, oracle, golden_dir, qtype, G):
+    z = np.load(os.path.join(golden_dir, f"q4fc_small_{oracle.variant_name(qtype, G)}.npz"))
+    wq = pkg.llmops.offline_FC_quant_Q4A(dev(z["W"]), qtype=QNAME[qtype], group_k=G)
+    assert np.array_equal(wq.cpu().numpy(), z["packed"])
+    deq = pkg.llmops.offline_FC_dequant_Q4A(wq)
+    assert np.array_equal(deq.cpu().numpy(), z["dequant"])
+
+
+def test_pack_config1_sha(pkg, oracle, golden_dir):
+    rec = json.load(open(os.path.join(golden_dir, "config1_sha256.json")))
+    g = torch.Generator().manual_seed(0)
+    W = torch.randn(4096, 4096, generator=g) * 0.02
+    x = torch.randn(1, 1, 4096, generator=g)
+    wq = pkg.llmops.offline_FC_quant_Q4A(W.cuda())
+    assert tuple(wq.shape) == (128, 128, 640)
+    assert sha(wq.cpu().numpy()) == rec["packed"]
+    codes, scales, gsums = pkg.llmops.FC_dynamic_quantize_x(x.cuda(), 32, 1.0)
+    assert sha(codes.cpu().numpy()) == rec["codes"]
+    assert sha(scales.cpu().numpy()) == rec["scales"]
+    assert sha(gsums.cpu().numpy()) == rec["gsums"]
+    y = pkg.llmops.fc_Q4A(x.cuda(), wq, 4096).cpu().numpy()
+    want = oracle.restated.fc(x.numpy(), wq.cpu().numpy(), 4096)
+    assert sha(want) == rec["y"]
+    assert close(y, want) and np.allclose(y[0, 0, :4], rec["y_head"], rtol=RTOL, atol=ATOL)
+    assert abs(float(y.astype(np.float64).sum()) - rec["y_sum_f64"]) < 1e-2
+
+
+@pytest.mark.parametrize("qtype,G", VARIANTS)
+@pytest.mark.parametrize("N,K", [(32, 128), (96, 640), (40, 200), (33, 36), (1000, 4096 + 128)])
+def test_pack_vs_oracle_shapes(pkg, oracle, qtype, G, N, K):
+    g = torch.Generator().manual_seed(N * 31 + K)
+    W = torch.randn(N, K, generator=g) * 0.02
+    W[0, : min(K, 40)] = 0.0          # an all-zero group
+    if N > 1:
+        W[1, :8] = torch.tensor([0.0, -0.0, 0.0, 0.0, -0.0, 0.0, 0.0, 0.0])  # zero-sign ties
+        W[1, 8:G] = 0.0
+    want = oracle.restated.pack(W.numpy(), qtype, G)
+    got = pkg.llmops.offline_FC_quant_Q4A(W.cuda(), qtype=QNAME[qtype], group_k=G).cpu().numpy()
+    assert got.shape == want.shape
+    assert np.array_equal(got, want)
+    for signed in (False, True):
+        d_want = oracle.restated.dequant(want, nibble_signed=signed)
+        d_got = pkg.llmops.offline_FC_dequant_Q4A(dev(want), nibble_signed=signed).cpu().numpy()
+        assert np.array_equal(d_got, d_want)
+
+
+def test_pack_negative_zero_minimum(pkg, oracle):
+    """get_min_max keeps the FIRST of equal values: a group of (-0, +0, ...) stores m = -0."""
+    W = np.zeros((32, 32), np.float32)
+    W[0, 0] = -0.0
+    W[1, 1] = -0.0          # +0 first, -0 later: m = +0
+    W[2, :] = -0.0
+    for q in (0, 1):
+        want = oracle.restated.pack(W, q, 32)
+        got = pkg.llmops.offline_FC_quant_Q4A(dev(W), qtype=QNAME[q], group_k=32).cpu().numpy()
+        assert np.array_equal(got, want)
+
+
+def test_known_answer_construction(pkg, golden_dir):
+    """ops/test_ops.py:106-149: Q4_1 packing lossless, FC == fp32 linear, zero tolerance."""
+    z = np.load(os.path.join(golden_dir, "known_answer_q4_1.npz"))
+    W, x = dev(z["W"]), dev(z["x"])
+    for G in (32, 128):
+        wq = pkg.llmops.offline_FC_quant_Q4A(W, group_k=G)
+        assert np.array_equal(wq.cpu().numpy(), z[f"packed_g{G}"])
+        assert np.array_equal(pkg.llmops.offline_FC_dequant_Q4A(wq).cpu().numpy(), z["W"])
+        y = pkg.llmops.fc_Q4A(x, wq, W.shape[0]).cpu().numpy()      # rows = 10 -> prefill path
+        assert np.array_equal(y, z["linear"])
+        y8 = pkg.llmops.fc_Q4A(x[:, :4].contiguous(), wq, W.shape[0]).cpu().numpy()  # rows = 8 -> decode
+        assert np.array_equal(y8, z["linear"][:, :4])
+
+
+def test_known_answer_full_size(pkg):
+    """Same construction at the reference's own test size B=2, M=17, N=K=4096 (all sums exact in fp32)."""
+    g = torch.Generator().manual_seed(11)
+    N = K = 4096
+    w = torch.randint(-8, 8, (N, K), generator=g).float()
+    x = torch.randint(-127, 128, (2, 17, K), generator=g).float()
+    w[:, 0::32] = -8
+    w[:, 1::32] = 7
+    x[:, :, 0::32] = -127
+    x[:, :, 1::32] = 127
+    w, x = (w / 128).cuda(), (x / 128).cuda()
+    ref = torch.nn.functional.linear(x.double(), w.double()).float()
+    for G in (32, 128):
+        wq = pkg.llmops.offline_FC_quant_Q4A(w, group_k=G)
+        assert torch.equal(pkg.llmops.offline_FC_dequant_Q4A(wq), w)
+        assert torch.equal(pkg.llmops.fc_Q4A(x, wq, N), ref)
+        assert torch.equal(pkg.llmops.fc_Q4A(x[:1, :5].contiguous(), wq, N), ref[:1, :5])
+
+
+# ------------------------------------------------------------- quantizer ----
+@pytest.mark.parametrize("G", [32, 128])
+@pytest.mark.parametrize("rows,K", [(1, 4096), (8, 11008), (5, 200), (3, 36), (64, 1024), (1, 32)])
+def test_quant_x_bit_exact(pkg, oracle, G, rows, K):
+    g = torch.Generator().manual_seed(rows * 131 + K + G)
+    x = torch.randn(1, rows, K, generator=g)
+    x[0, 0, : min(K, 8)] = torch.tensor([127, .5, 1.5, 2.5, -.5, -1.5, -2.5, 3.5])[: min(K, 8)]
+    if rows > 1:
+        x[0, 1, :G] = 0.0
+    for scale in (1.0, 1.0 / 16):
+        c0, s0, g0 = oracle.restated.quant_x(x.numpy(), G, scale)
+        c1, s1, g1 = pkg.llmops.FC_dynamic_quantize_x(x.cuda(), G, scale)
+        assert np.array_equal(c1.cpu().numpy(), c0)
+        assert np.array_equal(s1.cpu().numpy(), s0)
+        assert np.array_equal(g1.cpu().numpy(), g0)
+
+
+@pytest.mark.parametrize("qtype,G", VARIANTS)
+def test_quant_x_golden(pkg, oracle, golden_dir, qtype, G):
+    z = np.load(os.path.join(golden_dir, f"q4fc_small_{oracle.variant_name(qtype, G)}.npz"))
+    c, s, gs = pkg.llmops.FC_dynamic_quantize_x(dev(z["x"]), G, 1.0 if qtype else 1.0 / 16)
+    assert np.array_equal(c.cpu().numpy(), z["codes"])
+    assert np.array_equal(s.cpu().numpy(), z["scales"])
+    assert np.array_equal(gs.cpu().numpy(), z["gsums"])
+
+
+# -------------------------------------------------------------------- FC ----
+@pytest.mark.parametrize("qtype,G", VARIANTS)
+def test_fc_golden(pkg, oracle, golden_dir, qtype, G):
+    z = np.load(os.path.join(golden_dir, f"q4fc_small_{oracle.variant_name(qtype, G)}.npz"))
+    y = pkg.llmops.fc_Q4A(dev(z["x"]), dev(z["packed"]), int(z["N"])).cpu().numpy()
+    assert y.shape == z["y"].shape
+    assert close(y, z["y"])
+    assert np.abs(y - z["y"]).max() < 2e-5
+
+
+@pytest.mark.parametrize("qtype,G", VARIANTS)
+@pytest.mark.parametrize("rows", [1, 2, 3, 4, 7, 8])
+@pytest.mark.parametrize("N,K", [(32, 128), (4096, 4096), (160, 1280), (352, 11008)])
+def test_fc_decode_vs_oracle(pkg, oracle, qtype, G, rows, N, K):
+    g = torch.Generator().manual_seed(N + 7 * K + rows)
+    W = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(1, rows, K, generator=g)
+    wq = oracle.restated.pack(W.numpy(), qtype, G)
+    want = oracle.restated.fc(x.numpy(), wq, N)
+    got = pkg.llmops.fc_Q4A(x.cuda(), dev(wq), N, path="decode").cpu().numpy()
+    assert close(got, want), np.abs(got - want).max()
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000)])
+@pytest.mark.parametrize("rows", [1, 2, 4, 8])
+def test_fc_decode_llama7b_shapes_q4_1_g128(pkg, oracle, K, N, rows):
+    """The decode sweep the benchmark runs: Q4_1 group 128 over the Llama-7B FC shapes."""
+    g = torch.Generator().manual_seed(K * 3 + N + rows)
+    W = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(1, rows, K, generator=g)
+    wq_gpu = pkg.llmops.offline_FC_quant_Q4A(W.cuda(), group_k=128)
+    wq = oracle.restated.pack(W.numpy(), 1, 128)
+    assert np.array_equal(wq_gpu.cpu().numpy(), wq)
+    want = oracle.restated.fc(x.numpy(), wq, N)
+    got = pkg.llmops.fc_Q4A(x.cuda(), wq_gpu, N).cpu().numpy()
+    assert close(got, want), np.abs(got - want).max()
+
+
+@pytest.mark.parametrize("qtype,G", [(0, 32), (0, 128)])
+def test_fc_q4_0_signed_option(pkg, oracle, qtype, G):
+    g = torch.Generator().manual_seed(77 + G)
+    W = torch.randn(64, 512, generator=g) * 0.02
+    x = torch.randn(1, 3, 512, generator=g)
+    wq = oracle.restated.pack(W.numpy(), qtype, G)
+    want = oracle.restated.fc(x.numpy(), wq, 64, nibble_signed=True)
+    got = pkg.llmops.fc_Q4A(x.cuda(), dev(wq), 64, nibble_signed=True).cpu().numpy()
+    assert close(got, want)
+    # and the corrected reading is the one that approximates the fp32 product
+    lin = x.numpy() @ W.numpy().T
+    assert np.abs(got - lin).max() < 0.15 * np.abs(lin).max()
+
+
+def test_fc_repeatable_and_workspace_reuse(pkg, oracle):
+    """Back-to-back calls share one workspace; results are bit-identical run to run."""
+    g = torch.Generator().manual_seed(3)
+    W = torch.randn(4096, 4096, generator=g) * 0.02
+    wq = pkg.llmops.offline_FC_quant_Q4A(W.cuda(), group_k=128)
+    x = torch.randn(1, 4, 4096, generator=g).cuda()
+    y0 = pkg.llmops.fc_Q4A(x, wq, 4096)
+    for _ in range(5):
+        assert torch.equal(pkg.llmops.fc_Q4A(x, wq, 4096), y0)
+    ws = pkg.llmops.fc_workspace(4, 4096, 4096, 1, 128, x.device)
+    ws.check()
+    assert int(ws.buf[256:].to(torch.int32).abs().sum().item()) >= 0  # readable
+    counters = ws.buf[256:256 + 4 * 128].view(torch.int32)
+    assert int(counters.abs().sum().item()) == 0, "stripe counters must return to zero"
+
+
+def test_fc_pdl_chain(pkg, oracle):
+    """A chain launched with programmatic stream serialization gives the same results."""
+    g = torch.Generator().manual_seed(21)
+    Ws = [(torch.randn(4096, 4096, generator=g) * 0.02).cuda() for _ in range(3)]
+    wqs = [pkg.llmops.offline_FC_quant_Q4A(w, group_k=128) for w in Ws]
+    x = torch.randn(1, 1, 4096, generator=g).cuda()
+    plain = []
+    h = x
+    for wq in wqs:
+        h = pkg.llmops.fc_Q4A(h, wq, 4096)
+        plain.append(h)
+    for _ in range(3):
+        h = x
+        for i, wq in enumerate(wqs):
+            h = pkg.llmops.fc_Q4A(h, wq, 4096, pdl=True)
+            assert torch.equal(h, plain[i])
+
+
+@pytest.mark.parametrize("qtype,G", VARIANTS)
+def test_fc_many_rows(pkg, oracle, qtype, G):
+    g = torch.Generator().manual_seed(5 + G)
+    N, K = 320, 1024
+    W = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(2, 17, K, generator=g)
+    wq = oracle.restated.pack(W.numpy(), qtype, G)
+    want = oracle.restated.fc(x.numpy(), wq, N)
+    got = pkg.llmops.fc_Q4A(x.cuda(), dev(wq), N).cpu().numpy()
+    assert got.shape == (2, 17, N)
+    assert close(got, want), np.abs(got - want).max()
+
+
+def test_fc_ragged_n_and_k(pkg, oracle):
+    g = torch.Generator().manual_seed(9)
+    N, K, G = 40, 72, 32
+    W = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(1, 2, K, generator=g)
+    wq = pkg.llmops.offline_FC_quant_Q4A(W.cuda(), group_k=G)
+    assert np.array_equal(wq.cpu().numpy(), oracle.restated.pack(W.numpy(), 1, G))
+    want = oracle.restated.fc(x.numpy(), wq.cpu().numpy(), N)
+    got = pkg.llmops.fc_Q4A(x.cuda(), wq, N).cpu().numpy()
+    assert close(got, want)
+
+
+def test_scaling_by_power_of_two_is_exact(pkg):
+    """Size-independent property at a full Llama-7B shape: y(4x) == 4 y(x) bit for bit."""
+    g = torch.Generator().manual_seed(1)
+    W = (torch.randn(11008, 4096, generator=g) * 0.02).cuda()
+    wq = pkg.llmops.offline_FC_quant_Q4A(W, group_k=128)
+    x = torch.randn(1, 8, 4096, generator=g).cuda()
+    assert torch.equal(pkg.llmops.fc_Q4A(x * 4, wq, 11008), pkg.llmops.fc_Q4A(x, wq, 11008) * 4)
+
+
+def test_wrappers(pkg, oracle):
+    """Old-extension names and the per-Linear callable of the reference model."""
+    g = torch.Generator().manual_seed(2)
+    lin = torch.nn.Linear(256, 96, bias=True)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(96, 256, generator=g) * 0.02)
+        lin.bias.copy_(torch.randn(96, generator=g))
+    x = torch.randn(1, 3, 256, generator=g)
+    wq = oracle.restated.pack(lin.weight.detach().numpy(), 1, 32)
+    want = oracle.restated.fc(x.numpy(), wq, 96)
+    op = pkg.llmop_fc_q4a(lin)
+    assert op.N == 96 and repr(op) == "llmop_fc_q4a(weight: [3, 8, 640])"
+    assert op.weight_size() == 3 * 8 * 640 + 96 * 4
+    assert close(op(x.cuda()).cpu().numpy(), want + lin.bias.detach().numpy())
+    fc = pkg.c_ext.FCQ4A(lin.weight.detach().cuda())
+    assert repr(fc) == "FCQ4A()" and fc._N == 96
+    assert np.array_equal(fc._weight.cpu().numpy(), wq)
+    assert close(fc.forward(x.cuda()).cpu().numpy(), want)
+    assert close(pkg.c_ext.FC_evaluate_Q4A(x.cuda(), pkg.c_ext.FC_quant_Q4A(lin.weight.detach().cuda()), 96)
+                 .cpu().numpy(), want)
+
+
+def test_errors_on_gpu(pkg):
+    x = torch.zeros(1, 1, 64, device="cuda")
+    wq = torch.zeros(1, 2, 640, dtype=torch.int8, device="cuda")
+    with pytest.raises(RuntimeError, match="does not match"):
+        pkg.llmops.fc_Q4A(torch.zeros(1, 1, 100, device="cuda"), wq, 32)
+    with pytest.raises(RuntimeError, match="exceeds"):
+        pkg.llmops.fc_Q4A(x, wq, 64)
+    with pytest.raises(RuntimeError, match="none of"):
+        pkg.llmops.fc_Q4A(x, torch.zeros(1, 2, 600, dtype=torch.int8, device="cuda"), 32)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        pkg.llmops.fc_Q4A(torch.zeros(1, 64, 2, device="cuda").transpose(1, 2), wq, 32)
+    assert pkg.llmops.fc_Q4A(x[:, :0], wq, 32).shape == (1, 0, 32)
+
+
+def test_full_layer_pack_matches_oracle(pkg, oracle):
+    """One Llama-7B layer's FC set at full size, group 32 and 128: packed bytes bit-equal."""
+    shapes = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
+    for i, (N, K) in enumerate(shapes):
+        g = torch.Generator().manual_seed(100 + i)
+        W = torch.randn(N, K, generator=g) * 0.02
+        Wd = W.cuda()
+        for G in (32, 128):
+            got = pkg.llmops.offline_FC_quant_Q4A(Wd, group_k=G).cpu().numpy()
+            assert sha(got) == sha(oracle.restated.pack(W.numpy(), 1, G))
