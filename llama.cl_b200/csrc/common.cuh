@@ -41,9 +41,9 @@ struct DeviceInfo {
 const DeviceInfo* device_info();
 
 // ---- workspace layout of the FC entry points ------------------------------
-// [0, 256)            status word (int) + padding
-// [256, 256+4*NgMax)  per-stripe arrival counters (int), zero between calls
-// then                CTA partials: [ctas][2][8][32] fp32
+// [0, 256)   status word (int) + padding
+// then       CTA partials [ctas][2][8][32] fp32 (size fixed per device)
+// then       per-stripe arrival counters int[Ng], zero between calls
 constexpr size_t kWsStatusBytes = 256;
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }

@@ -412,11 +412,17 @@ constexpr int kCtasPerSm = 2;
 
 }  // namespace
 
-size_t decode_workspace_bytes(int64_t N) {
+// Workspace layout (the same for every call, so that one workspace serves calls of any N):
+//   [0, 256) status | CTA partials [ctas][2][8][32] fp32 | stripe counters int[Ng]
+static size_t partials_bytes() {
     const DeviceInfo* di = device_info();
     const int sms = di ? di->sm_count : 256;
+    return (size_t)sms * kCtasPerSm * 2 * 256 * sizeof(float);
+}
+
+size_t decode_workspace_bytes(int64_t N) {
     const int64_t Ng = (N + 31) / 32;
-    return kWsStatusBytes + align_up((size_t)Ng * 4, 256) + (size_t)sms * kCtasPerSm * 2 * 256 * sizeof(float);
+    return kWsStatusBytes + partials_bytes() + align_up((size_t)Ng * 4, 256);
 }
 
 int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
@@ -435,8 +441,8 @@ int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uin
     }
     DecodeParams p;
     p.x = x, p.y = y, p.wq = wq;
-    p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kWsStatusBytes);
-    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kWsStatusBytes + align_up((size_t)Ng * 4, 256));
+    p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + kWsStatusBytes);
+    p.counters = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kWsStatusBytes + partials_bytes());
     p.K = K, p.ldx = ldx, p.N = N, p.ldy = ldy;
     p.rows = rows, p.Ng = (int)Ng, p.Kg = (int)Kg, p.T = (int)(Ng * Kg);
     const int64_t Kp = Kg * G;

@@ -222,9 +222,25 @@ def test_fc_repeatable_and_workspace_reuse(pkg, oracle):
         assert torch.equal(pkg.llmops.fc_Q4A(x, wq, 4096), y0)
     ws = pkg.llmops.fc_workspace(4, 4096, 4096, 1, 128, x.device)
     ws.check()
-    assert int(ws.buf[256:].to(torch.int32).abs().sum().item()) >= 0  # readable
-    counters = ws.buf[256:256 + 4 * 128].view(torch.int32)
+    counters = ws.buf[ws.nbytes - 4 * 128:].view(torch.int32)   # the counters close the workspace
     assert int(counters.abs().sum().item()) == 0, "stripe counters must return to zero"
+
+
+def test_fc_workspace_shared_between_shapes(pkg, oracle):
+    """One workspace serves interleaved calls of different N (fixed layout)."""
+    g = torch.Generator().manual_seed(4)
+    shapes = [(64, 256), (4096, 4096), (32, 128), (11008, 4096)]
+    ws = pkg.llmops.Workspace(pkg._cabi.lib().q4fc_fc_workspace_bytes(8, 4096, 11008, 1, 128), torch.device("cuda"))
+    cases = []
+    for N, K in shapes:
+        W = torch.randn(N, K, generator=g) * 0.02
+        x = torch.randn(1, 3, K, generator=g)
+        wq = oracle.restated.pack(W.numpy(), 1, 128)
+        cases.append((x.cuda(), dev(wq), N, oracle.restated.fc(x.numpy(), wq, N)))
+    for _ in range(2):
+        for x, wq, N, want in cases:
+            got = pkg.llmops.fc_Q4A(x, wq, N, workspace=ws).cpu().numpy()
+            assert close(got, want), (N, np.abs(got - want).max())
 
 
 def test_fc_pdl_chain(pkg, oracle):
