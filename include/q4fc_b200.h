@@ -119,6 +119,21 @@ int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq
             int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
             q4fc_stream_t stream);
 
+/* No counterpart in the reference.  q4fc_fc_decode for callers that cannot
+ * allocate device memory -- hosts that give all of it to their own arena at
+ * start-up, or that run under a budget where a late cudaMalloc may fail or
+ * stall the device.  The reduction scratch is a fixed array inside the
+ * library image (about 1.3 MB per GPU that loads the library, held until the
+ * process exits), so no workspace is passed and nothing is allocated.
+ * Limits: rows <= 8, N <= 262144, at most 320 SMs; beyond them the call
+ * returns Q4FC_ELIMIT.  All calls on a device share the array: calls that may
+ * overlap on the GPU race, so keep them ordered on one stream (or by events).
+ * The first call on a device looks up the array's address; make it outside
+ * any stream capture.  Results are identical to q4fc_fc_decode. */
+int q4fc_fc_decode_noalloc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng,
+                           int64_t Kg, int qtype, int group_k, int64_t N, float* y, int64_t ldy, unsigned flags,
+                           q4fc_stream_t stream);
+
 /* Reads and clears the device status word kept at the start of a workspace
  * (host-synchronous: waits for `stream`).  Returns Q4FC_OK or Q4FC_EDEVICE. */
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream);

@@ -19,7 +19,7 @@ FLAG_PDL = 2
 SYMBOLS = (
     "q4fc_version", "q4fc_strerror", "q4fc_last_error", "q4fc_block_bytes", "q4fc_infer_variant",
     "q4fc_pack", "q4fc_dequant", "q4fc_quant_x", "q4fc_fc_workspace_bytes", "q4fc_fc_workspace_init",
-    "q4fc_fc_decode", "q4fc_fc_prefill", "q4fc_fc", "q4fc_fc_check_status",
+    "q4fc_fc_decode", "q4fc_fc_prefill", "q4fc_fc", "q4fc_fc_check_status", "q4fc_fc_decode_noalloc",
 )
 
 _lib = None
@@ -51,6 +51,7 @@ def lib() -> C.CDLL:
     for name in ("q4fc_fc_decode", "q4fc_fc_prefill", "q4fc_fc"):
         getattr(L, name).argtypes = fc_args
     L.q4fc_fc_check_status.argtypes = [vp, vp]
+    L.q4fc_fc_decode_noalloc.argtypes = [vp, i64, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, u32, vp]
     _lib = L
     return L
 

@@ -469,3 +469,95 @@ int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uin
 }
 
 }  // namespace q4fc
+
+// ---------------------------------------------------------------------------
+// Decode FC for callers that cannot allocate device memory.
+//
+// Some hosts of this library hand every byte of device memory to their own
+// arena when the process starts (serving runtimes that size their KV cache
+// from "whatever is free"), or run under a memory budget in which a late
+// cudaMalloc can fail or stall the device while it synchronizes.  Such a
+// caller has nowhere to get the FC workspace from.  For it the partial sums
+// and arrival counters of the stream-K reduction live in a fixed array that
+// is part of the loaded library image: every GPU that loads the library
+// holds kStaticScratchBytes (about 1.3 MB) until the process exits.
+//
+// The array is shared by every call on a device and keeps what the last call
+// left in it.  The counters and the status word are cleared on the stream
+// before each launch.  Two calls that may overlap on the GPU (different
+// streams without an ordering between them) race on the array; order them.
+//
+// The first call on a device looks up the array's device address; make that
+// first call outside any stream capture.
+#include <mutex>
+
+namespace q4fc {
+namespace {
+constexpr int kStaticMaxCtas = 640;        // room for 320 SMs at two CTAs each
+constexpr int64_t kStaticMaxN = 262144;    // 8192 stripes of 32 columns
+constexpr size_t kStaticScratchBytes =
+    kWsStatusBytes + (size_t)kStaticMaxCtas * 2 * 256 * sizeof(float) + (size_t)(kStaticMaxN / 32) * sizeof(int);
+}  // namespace
+}  // namespace q4fc
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_static_scratch[q4fc::kStaticScratchBytes];
+
+extern "C" __attribute__((visibility("default"))) int q4fc_fc_decode_noalloc(
+    const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg, int qtype,
+    int group_k, int64_t N, float* y, int64_t ldy, unsigned flags, q4fc_stream_t stream) {
+    using namespace q4fc;
+    static std::mutex mu;
+    static void* dev_ptr[64] = {};
+    if (!valid_variant(qtype, group_k)) {
+        set_error("fc_decode_noalloc: unsupported block type (qtype=%d, group_k=%d)", qtype, group_k);
+        return Q4FC_EVARIANT;
+    }
+    if (rows < 0 || rows > kMaxDecodeRows || K <= 0 || N < 0 || Kg <= 0 || (K + group_k - 1) / group_k != Kg ||
+        N > Ng * 32 || ldx < K || ldy < N || (rows > 0 && N > 0 && (!x || !wq || !y))) {
+        set_error("fc_decode_noalloc: bad sizes or null pointer (rows=%lld<=8, K=%lld, Kg=%lld, N=%lld, Ng=%lld)",
+                  (long long)rows, (long long)K, (long long)Kg, (long long)N, (long long)Ng);
+        return Q4FC_EINVAL;
+    }
+    if ((reinterpret_cast<uintptr_t>(wq) & 15) || (reinterpret_cast<uintptr_t>(x) & 3) ||
+        (reinterpret_cast<uintptr_t>(y) & 3)) {
+        set_error("fc_decode_noalloc: packed weights need 16-byte alignment, x and y 4-byte");
+        return Q4FC_EALIGN;
+    }
+    if (N > kStaticMaxN) {
+        set_error("fc_decode_noalloc: N=%lld exceeds the built-in scratch (N <= %lld); use q4fc_fc_decode with a "
+                  "caller-provided workspace", (long long)N, (long long)kStaticMaxN);
+        return Q4FC_ELIMIT;
+    }
+    if (rows == 0 || N == 0) return Q4FC_OK;
+    const size_t need = decode_workspace_bytes(N);
+    if (need > kStaticScratchBytes) {
+        set_error("fc_decode_noalloc: this GPU needs %zu bytes of scratch, the built-in array holds %zu", need,
+                  (size_t)kStaticScratchBytes);
+        return Q4FC_ELIMIT;
+    }
+    int dev = 0;
+    Q4FC_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("fc_decode_noalloc: device index %d not supported", dev);
+        return Q4FC_ELIMIT;
+    }
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev_ptr[dev] == nullptr) {
+            // set-up, once per device, with that device current
+            void* p = nullptr;
+            Q4FC_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+            dev_ptr[dev] = p;
+        }
+        scratch = dev_ptr[dev];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // what must start at zero: the status word and this call's stripe counters
+    Q4FC_CUDA_OK(cudaMemsetAsync(scratch, 0, kWsStatusBytes, s));
+    Q4FC_CUDA_OK(cudaMemsetAsync(static_cast<unsigned char*>(scratch) + need - align_up((size_t)((N + 31) / 32) * 4, 256),
+                                 0, align_up((size_t)((N + 31) / 32) * 4, 256), s));
+    return launch_fc_decode(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y, ldy,
+                            scratch, kStaticScratchBytes, flags, s);
+}
