@@ -75,6 +75,9 @@ def load_peaks() -> tuple[float, str]:
         return 6650.0, "fallback"
 
 
+_emit = print  # replaced in main() by a writer bound to the real stdout
+
+
 # --------------------------------------------------------------------- clocks
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
@@ -199,7 +202,7 @@ def reference_arm(args) -> None:
                                    f"{ncpu} logical CPUs, {cores} OpenMP threads"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    _emit(json.dumps(line))
 
 
 # ------------------------------------------------------------------- our arm
@@ -449,17 +452,24 @@ def our_arm(args) -> None:
             "clocks": clocks, "e2e": e2e, "gpu_launches": len(calls) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "fc_decode_kernel<128,1,false>",
+                         "kernel": "fc_decode_cluster_kernel<128,1,false,ROWS>",
                          "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": len(calls)},
             "cpu_baseline": cpu_baseline, "parity_spot_check": check, "fc_stack": stack,
         }
-        print(json.dumps(line), flush=True)
+        _emit(json.dumps(line))
     if distributed:
         dist.barrier()
         dist.destroy_process_group()
 
 
 def main() -> None:
+    # The checker libraries (the compiled reference prints a banner per thread pool) and any
+    # library chatter must not reach stdout: the one JSON line goes to the real stdout, the
+    # rest of the process writes to stderr.
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    global _emit
+    _emit = lambda line: (real_stdout.write(line + "\n"), real_stdout.flush())  # noqa: E731
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)

@@ -60,7 +60,12 @@ enum {
      * outputs and workspace only after the predecessor has completed, and
      * streams weights before that.  Use only when the predecessor does not
      * write this call's weights. */
-    Q4FC_FLAG_PDL = 2u
+    Q4FC_FLAG_PDL = 2u,
+    /* q4fc_fc_decode only: use the stream-K kernel (one contiguous byte run
+     * per CTA, partial sums through the workspace) instead of the default
+     * cluster kernel (partial sums through distributed shared memory, no
+     * workspace needed).  Same results within rounding of the fp32 sums. */
+    Q4FC_FLAG_STREAMK = 4u
 };
 
 int q4fc_version(void);
@@ -106,7 +111,8 @@ int q4fc_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int group
  * ws: workspace of at least q4fc_fc_workspace_bytes() bytes, 256-byte
  * aligned, zeroed once with q4fc_fc_workspace_init() before its first use;
  * the kernels leave it ready for the next call.  Calls that may overlap on
- * the GPU need separate workspaces. */
+ * the GPU need separate workspaces.  q4fc_fc_decode without
+ * Q4FC_FLAG_STREAMK does not touch it and accepts ws = NULL. */
 size_t q4fc_fc_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int group_k);
 int q4fc_fc_workspace_init(void* ws, size_t ws_bytes, q4fc_stream_t stream);
 int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libq4fc_b200.so")
 Q4_0, Q4_1 = 0, 1
 FLAG_NIBBLE_SIGNED = 1
 FLAG_PDL = 2
+FLAG_STREAMK = 4
 
 # every symbol declared in include/q4fc_b200.h
 SYMBOLS = (

@@ -235,8 +235,11 @@ int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const v
         set_error("fc_decode: workspace needs 256-byte alignment");
         return Q4FC_EALIGN;
     }
-    return launch_fc_decode(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y, ldy,
-                            ws, ws_bytes, flags, static_cast<cudaStream_t>(stream));
+    if (flags & Q4FC_FLAG_STREAMK)
+        return launch_fc_decode(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y,
+                                ldy, ws, ws_bytes, flags, static_cast<cudaStream_t>(stream));
+    return launch_fc_decode_cluster(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N,
+                                    y, ldy, flags, static_cast<cudaStream_t>(stream));
 }
 
 int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,

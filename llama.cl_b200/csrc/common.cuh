@@ -58,6 +58,11 @@ size_t decode_workspace_bytes(int64_t N);
 int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
                      int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
                      cudaStream_t s);
+// cluster form of the decode kernel (no global scratch)
+int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
+                             int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
+                             cudaStream_t s);
+int choose_cluster_count(int64_t Ng, int64_t nc_cap);
 size_t prefill_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int G);
 int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                       int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,

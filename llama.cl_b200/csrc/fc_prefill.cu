@@ -16,8 +16,9 @@ int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, cons
                       unsigned flags, cudaStream_t s) {
     for (int64_t r = 0; r < rows; r += kMaxDecodeRows) {
         const int n = (int)((rows - r < kMaxDecodeRows) ? rows - r : kMaxDecodeRows);
-        int rc = launch_fc_decode(x + r * ldx, n, K, ldx, wq, Ng, Kg, qtype, G, N, y + r * ldy, ldy, ws, ws_bytes,
-                                  flags & ~Q4FC_FLAG_PDL, s);
+        (void)ws, (void)ws_bytes;
+        int rc = launch_fc_decode_cluster(x + r * ldx, n, K, ldx, wq, Ng, Kg, qtype, G, N, y + r * ldy, ldy,
+                                          flags & ~Q4FC_FLAG_PDL, s);
         if (rc) return rc;
     }
     return Q4FC_OK;

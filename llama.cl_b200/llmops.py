@@ -20,7 +20,7 @@ from __future__ import annotations
 import torch
 
 from . import _cabi
-from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, Q4_0, Q4_1
+from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, FLAG_STREAMK, Q4_0, Q4_1
 
 __all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
            "fc_workspace", "Workspace"]
@@ -145,7 +145,8 @@ def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_s
 
     input fp32 ``[B, M, K]``, wei_quantized int8 ``[Ng, Kg, block_bytes]`` ->
     fp32 ``[B, M, N]``.  ``path``: "auto" (decode kernel for B*M <= 8, else
-    the prefill kernel), "decode" or "prefill"."""
+    the prefill kernel), "decode", "streamk" (the decode kernel that reduces
+    through the workspace) or "prefill"."""
     _require_cuda(input, "input", torch.float32, 3)
     _require_cuda(wei_quantized, "wei_quantized", torch.int8, 3)
     if wei_quantized.device != input.device:
@@ -164,8 +165,11 @@ def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_s
     if workspace is None:
         workspace = fc_workspace(rows, K, N, q, G, input.device)
     flags = (FLAG_NIBBLE_SIGNED if nibble_signed else 0) | (FLAG_PDL if pdl else 0)
+    if path == "streamk":
+        flags |= FLAG_STREAMK
     L = _cabi.lib()
-    fn = {"auto": L.q4fc_fc, "decode": L.q4fc_fc_decode, "prefill": L.q4fc_fc_prefill}[path]
+    fn = {"auto": L.q4fc_fc, "decode": L.q4fc_fc_decode, "streamk": L.q4fc_fc_decode,
+          "prefill": L.q4fc_fc_prefill}[path]
     with torch.cuda.device(input.device):
         _cabi.check(fn(input.data_ptr(), rows, K, K, wei_quantized.data_ptr(), Ng, Kg, q, G, N, out.data_ptr(), N,
                        workspace.ptr, workspace.nbytes, flags, _stream_ptr(input.device)), "fc_Q4A")

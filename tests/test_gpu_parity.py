@@ -168,16 +168,17 @@ def test_fc_golden(pkg, oracle, golden_dir, qtype, G):
     assert np.abs(y - z["y"]).max() < 2e-5
 
 
+@pytest.mark.parametrize("path", ["decode", "streamk"])
 @pytest.mark.parametrize("qtype,G", VARIANTS)
 @pytest.mark.parametrize("rows", [1, 2, 3, 4, 7, 8])
-@pytest.mark.parametrize("N,K", [(32, 128), (4096, 4096), (160, 1280), (352, 11008)])
-def test_fc_decode_vs_oracle(pkg, oracle, qtype, G, rows, N, K):
+@pytest.mark.parametrize("N,K", [(32, 128), (4096, 4096), (160, 1280), (352, 11008), (2080, 640)])
+def test_fc_decode_vs_oracle(pkg, oracle, path, qtype, G, rows, N, K):
     g = torch.Generator().manual_seed(N + 7 * K + rows)
     W = torch.randn(N, K, generator=g) * 0.02
     x = torch.randn(1, rows, K, generator=g)
     wq = oracle.restated.pack(W.numpy(), qtype, G)
     want = oracle.restated.fc(x.numpy(), wq, N)
-    got = pkg.llmops.fc_Q4A(x.cuda(), dev(wq), N, path="decode").cpu().numpy()
+    got = pkg.llmops.fc_Q4A(x.cuda(), dev(wq), N, path=path).cpu().numpy()
     assert close(got, want), np.abs(got - want).max()
     assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
 
@@ -217,9 +218,10 @@ def test_fc_repeatable_and_workspace_reuse(pkg, oracle):
     W = torch.randn(4096, 4096, generator=g) * 0.02
     wq = pkg.llmops.offline_FC_quant_Q4A(W.cuda(), group_k=128)
     x = torch.randn(1, 4, 4096, generator=g).cuda()
-    y0 = pkg.llmops.fc_Q4A(x, wq, 4096)
-    for _ in range(5):
-        assert torch.equal(pkg.llmops.fc_Q4A(x, wq, 4096), y0)
+    for path in ("decode", "streamk"):
+        y0 = pkg.llmops.fc_Q4A(x, wq, 4096, path=path)
+        for _ in range(5):
+            assert torch.equal(pkg.llmops.fc_Q4A(x, wq, 4096, path=path), y0)
     ws = pkg.llmops.fc_workspace(4, 4096, 4096, 1, 128, x.device)
     ws.check()
     counters = ws.buf[ws.nbytes - 4 * 128:].view(torch.int32)   # the counters close the workspace
@@ -239,7 +241,7 @@ def test_fc_workspace_shared_between_shapes(pkg, oracle):
         cases.append((x.cuda(), dev(wq), N, oracle.restated.fc(x.numpy(), wq, N)))
     for _ in range(2):
         for x, wq, N, want in cases:
-            got = pkg.llmops.fc_Q4A(x, wq, N, workspace=ws).cpu().numpy()
+            got = pkg.llmops.fc_Q4A(x, wq, N, workspace=ws, path="streamk").cpu().numpy()
             assert close(got, want), (N, np.abs(got - want).max())
 
 
@@ -254,11 +256,25 @@ def test_fc_pdl_chain(pkg, oracle):
     for wq in wqs:
         h = pkg.llmops.fc_Q4A(h, wq, 4096)
         plain.append(h)
+    # under programmatic serialization the kernel takes half of the CTA slots, so its fp32 sums are
+    # ordered differently: equal within tolerance to the plain chain, and bit-equal from run to run
+    first = None
     for _ in range(3):
         h = x
+        outs = []
         for i, wq in enumerate(wqs):
             h = pkg.llmops.fc_Q4A(h, wq, 4096, pdl=True)
-            assert torch.equal(h, plain[i])
+            outs.append(h)
+            assert close(h.cpu().numpy(), plain[i].cpu().numpy())
+        if first is None:
+            first = outs
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(outs, first))
+    for _ in range(2):
+        h = x
+        for i, wq in enumerate(wqs):
+            h = pkg.llmops.fc_Q4A(h, wq, 4096, pdl=True, path="streamk")
+            assert close(h.cpu().numpy(), plain[i].cpu().numpy())
 
 
 @pytest.mark.parametrize("qtype,G", VARIANTS)

@@ -9,8 +9,10 @@ workspace with cudaMalloc.  ``q4fc_fc_decode_noalloc`` keeps the reduction
 scratch in an array inside the library image instead.  The test calls it
 through the C-ABI twice in a row -- the second call finds the scratch as the
 first one left it -- and expects bit-identical outputs to ``q4fc_fc_decode``
-(same kernel, deterministic reduction order), which is inside the
-rtol 1e-3 / atol 1e-4 bar the other FC tests use.
+run with the same (stream-K) kernel and a caller-provided workspace, whose
+reduction order is deterministic; that is well inside the rtol 1e-3 /
+atol 1e-4 bar the other FC tests use, which is also checked against the
+default decode kernel.
 """
 import pytest
 import torch
@@ -24,8 +26,9 @@ def _call(L, fn_noalloc, x, wq, N, y, q, G, ws=None):
     s = torch.cuda.current_stream().cuda_stream
     if fn_noalloc:
         return L.q4fc_fc_decode_noalloc(x.data_ptr(), rows, K, K, wq.data_ptr(), Ng, Kg, q, G, N, y.data_ptr(), N, 0, s)
+    flags = 4 if ws is not None else 0  # Q4FC_FLAG_STREAMK: the kernel the allocation-free entry point runs
     return L.q4fc_fc_decode(x.data_ptr(), rows, K, K, wq.data_ptr(), Ng, Kg, q, G, N, y.data_ptr(), N,
-                            ws.data_ptr(), ws.numel(), 0, s)
+                            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, flags, s)
 
 
 @pytest.mark.parametrize("qname,q,G", [("q4_1", 1, 128), ("q4_1", 1, 32), ("q4_0", 0, 32)])
@@ -47,7 +50,9 @@ def test_noalloc_matches_workspace_entry_point(lib_built, qname, q, G):
             assert _call(L, True, x, wq, N, got, q, G) == 0, L.q4fc_last_error()
             torch.cuda.synchronize()
             assert torch.equal(got, want), (N, K, rows, call, float((got - want).abs().max()))
-            assert torch.allclose(got, want, rtol=1e-3, atol=1e-4)
+            default = torch.empty_like(want)
+            assert _call(L, False, x, wq, N, default, q, G, None) == 0, L.q4fc_last_error()
+            assert torch.allclose(got, default, rtol=1e-3, atol=1e-4)
 
 
 def test_noalloc_rejects_sizes_beyond_the_scratch(lib_built):
