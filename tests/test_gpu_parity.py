@@ -290,6 +290,51 @@ def test_fc_many_rows(pkg, oracle, qtype, G):
     assert close(got, want), np.abs(got - want).max()
 
 
+@pytest.mark.parametrize("qtype,G", VARIANTS)
+@pytest.mark.parametrize("rows,N,K", [(9, 32, 128), (130, 416, 1024), (256, 128, 4096), (300, 1000, 640), (5, 96, 256)])
+def test_fc_prefill_vs_oracle(pkg, oracle, qtype, G, rows, N, K):
+    """The tensor-core kernel on tile edges: partial row / column tiles, few and many K stages."""
+    g = torch.Generator().manual_seed(rows + 3 * N + 7 * K + G)
+    W = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(1, rows, K, generator=g)
+    wq = oracle.restated.pack(W.numpy(), qtype, G)
+    want = oracle.restated.fc(x.numpy(), wq, N)
+    got = pkg.llmops.fc_Q4A(x.cuda(), dev(wq), N, path="prefill").cpu().numpy()
+    assert close(got, want), np.abs(got - want).max()
+    assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    pkg.llmops.fc_workspace(rows, K, N, qtype, G, torch.device("cuda")).check()   # no wait ran out
+
+
+def test_fc_prefill_q4_0_signed(pkg, oracle):
+    g = torch.Generator().manual_seed(78)
+    W = torch.randn(160, 512, generator=g) * 0.02
+    x = torch.randn(1, 40, 512, generator=g)
+    for G in (32, 128):
+        wq = oracle.restated.pack(W.numpy(), 0, G)
+        want = oracle.restated.fc(x.numpy(), wq, 160, nibble_signed=True)
+        got = pkg.llmops.fc_Q4A(x.cuda(), dev(wq), 160, nibble_signed=True, path="prefill").cpu().numpy()
+        assert close(got, want), np.abs(got - want).max()
+
+
+def test_fc_prefill_config3_q4_0_g32(pkg, oracle):
+    """The prefill configuration of the baseline: Q4_0 group 32, M=512, K=4096, N=11008 (reference semantics)."""
+    g = torch.Generator().manual_seed(33)
+    N, K, M = 11008, 4096, 512
+    W = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(1, M, K, generator=g)
+    wq_gpu = pkg.llmops.offline_FC_quant_Q4A(W.cuda(), qtype="q4_0", group_k=32)
+    wq = oracle.restated.pack(W.numpy(), 0, 32)
+    assert np.array_equal(wq_gpu.cpu().numpy(), wq)
+    got = pkg.llmops.fc_Q4A(x.cuda(), wq_gpu, N).cpu().numpy()
+    rows = [0, 1, 127, 128, 300, 511]          # the oracle on a sample of rows keeps the test short
+    want = oracle.restated.fc(x.numpy()[:, rows], wq, N)
+    assert close(got[:, rows], want), np.abs(got[:, rows] - want).max()
+    # every row against the decode kernel (same arithmetic, different machinery)
+    for r0 in range(0, M, 8):
+        ref8 = pkg.llmops.fc_Q4A(x[:, r0:r0 + 8].cuda().contiguous(), wq_gpu, N, path="decode").cpu().numpy()
+        assert close(got[:, r0:r0 + 8], ref8)
+
+
 def test_fc_ragged_n_and_k(pkg, oracle):
     g = torch.Generator().manual_seed(9)
     N, K, G = 40, 72, 32
