@@ -22,13 +22,16 @@
 // work per (m, n, group) -- one int add, one fp add, one mul, one or two fma --
 // is what bounds this kernel: the tensor pipe waits for the epilogue.
 //
-// Warp roles (13 warps): 0-7 epilogue (warp%4 = TMEM lane quarter, warp/4 =
-// half of the 128 tile rows), 8-11 producers (unpack A, copy B and the scales
-// of one 128-k stage; generic-proxy stores + fence.proxy.async), 12 MMA issue
-// (one elected lane).  mbarriers: full/empty per shared-memory stage,
+// Warp roles (21 warps): 0-15 epilogue (warp%4 = TMEM lane quarter, warp/4 =
+// which 32 of the 128 tile rows), 16-19 producers (unpack A and stage the
+// scales of one 128-k stage: generic-proxy stores + fence.proxy.async; one of
+// them also issues the TMA load of the B tile from the code matrix), 20 MMA
+// issue (one elected lane).  mbarriers: full/empty per shared-memory stage,
 // tfull/tempty per TMEM buffer.  Every wait is bounded: when a wait runs out
 // the CTA sets the workspace status word, every role leaves its loop, TMEM is
 // freed and the kernel returns.
+#include <cuda.h>  // CUtensorMap and the cuTensorMapEncodeTiled prototype (resolved at run time, libcuda is not linked)
+
 #include "common.cuh"
 
 namespace q4fc {
@@ -39,7 +42,7 @@ constexpr int kTileM = 128;            // activation rows per tile = TMEM column
 constexpr int kStageK = 128;           // k per shared-memory stage (one 128-byte swizzle row)
 constexpr int kStages = 4;
 constexpr int kTmemBufs = 4;
-constexpr int kEpiWarps = 8, kProdWarps = 4;
+constexpr int kEpiWarps = 16, kProdWarps = 4;
 constexpr int kProdThreads = kProdWarps * 32;
 constexpr int kThreads = (kEpiWarps + kProdWarps + 1) * 32;
 constexpr int kMmaWarp = kEpiWarps + kProdWarps;
@@ -49,7 +52,7 @@ constexpr uint64_t kWaitLimitNs = 1000000000ull;  // every mbarrier wait gives u
 constexpr int kABytes = kTileN * kStageK;          // 16 KB
 constexpr int kBBytes = kTileM * kStageK;          // 16 KB
 constexpr int kWscBytes = 4 * kTileN * 8;          // [group in stage][n] {wd, wm} fp32
-constexpr int kXscBytes = 4 * kTileM * 8;          // [group in stage][m] {xs, gsum} fp32
+constexpr int kXscBytes = 4 * kTileM * 8;          // [group in stage][row pair] {xs0, xs1, gsum0, gsum1} fp32
 constexpr int kStageBytes = kABytes + kBBytes + kWscBytes + kXscBytes;  // 40 KB
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
@@ -103,6 +106,36 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     *abort_flag = 1;
     return false;
 }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// 2-D tiled TMA load (no multicast): box at (x, y) of the tensor map -> shared memory, completion on `bar`
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+// packed fp32 pairs (sm_100): one issue slot for two fused multiply-adds
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -143,7 +176,8 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t byte) {
 }
 
 template <int G, int QTYPE, bool SIGNED>
-__global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillParams p,
+                                                                 const __grid_constant__ CUtensorMap codes_map) {
     constexpr int BS = block_bytes(QTYPE, G);
     constexpr int GPS = kStageK / G;  // K groups per stage: 4 (group 32) or 1 (group 128)
     constexpr int MMAS = G / 32;      // K=32 instructions per group
@@ -164,7 +198,7 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; i++) {
-            mbar_init(bar_full + 8 * i, kProdThreads);
+            mbar_init(bar_full + 8 * i, kProdThreads + 1);  // producer threads + the TMA issuer's expect_tx
             mbar_init(bar_empty + 8 * i, 1 + kEpiWarps);
         }
         for (int i = 0; i < kTmemBufs; i++) {
@@ -192,71 +226,85 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
         const int c = lane & 7, rr = lane >> 3;       // 16-byte chunk (columns 4c..4c+3), row inside a 4-row set
         const int nb = nb0 + pw;
         const bool stripe_live = nb < p.Ng;
+        // columns are stored in a rotated order so that a half warp covers all 8 swizzle rows
+        // (conflict-free 8-byte stores); rows and the rotation do not change from stage to stage
+        uint32_t row_off[4];
+        int col_of[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            col_of[i] = (i + (c >> 1)) & 3;
+            const uint32_t row = pw * 32 + 4 * c + col_of[i];
+            row_off[i] = (row >> 3) * 1024 + (row & 7) * 128 + ((row & 7) << 16);  // low half: offset, high half: row&7
+        }
+        const uint8_t* stripe_base = p.wq + (int64_t)nb * p.Kg * BS;
+        const int64_t m_mine = m0 + pt;
         for (int it = 0; it < nstage; it++) {
             const int s = it % kStages;
             if (!mbar_wait(bar_empty + 8 * s, ((it / kStages) & 1) ^ 1, abort_flag)) break;
             uint8_t* st = smem + s * kStageBytes;
             const uint32_t a_base = smem_u32(st), b_base = a_base + kABytes;
             float2* wsc = reinterpret_cast<float2*>(st + kABytes + kBBytes);
-            float2* xsc = reinterpret_cast<float2*>(st + kABytes + kBBytes + kWscBytes);
+            float* xsc = reinterpret_cast<float*>(st + kABytes + kBBytes + kWscBytes);
             const int kb0 = it * GPS;
+            if (pt == 0) {  // B: 128 rows x 128 bytes of codes, swizzled by the TMA unit; rows beyond the matrix read 0
+                mbar_arrive_expect_tx(bar_full + 8 * s, kBBytes);
+                tma_load_2d(b_base, &codes_map, bar_full + 8 * s, it * kStageK, (int)m0);
+            }
             // ---- A: unpack nibbles of stripe nb: 16 word-rows (8 k each) x 32 columns
+            uint4 w[4];
 #pragma unroll
             for (int i4 = 0; i4 < 4; i4++) {
                 const int r = 4 * i4 + rr;  // word-row inside the stage: k = 8r .. 8r+7
-                uint4 w = make_uint4(0u, 0u, 0u, 0u);
-                const int kb = (G == 128) ? kb0 : kb0 + (r >> 2);
+                w[i4] = make_uint4(0u, 0u, 0u, 0u);
+                const int kb = (G == 128) ? kb0 : kb0 + i4;
                 if (stripe_live && kb < p.Kg) {
-                    const int row_in_block = (G == 128) ? r : (r & 3);
-                    w = ldg_stream_v4(p.wq + ((int64_t)nb * p.Kg + kb) * BS + row_in_block * 128 + c * 16);
+                    const int row_in_block = (G == 128) ? r : rr;
+                    w[i4] = ldg_stream_v4(stripe_base + (int64_t)kb * BS + row_in_block * 128 + c * 16);
                 }
-                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            }
+            // ---- scales of the stage's groups (loads issued before the unpack stores)
+            float2 wv[GPS];
+            float xv[GPS], gv[GPS];
+#pragma unroll
+            for (int gi = 0; gi < GPS; gi++) {
+                const int kb = kb0 + gi;
+                wv[gi] = make_float2(0.f, 0.f);
+                xv[gi] = 0.f, gv[gi] = 0.f;
+                if (kb < p.Kg) {
+                    if (stripe_live) {
+                        const uint8_t* tail = stripe_base + (int64_t)kb * BS + 16 * G;
+                        wv[gi].x = h2f(*reinterpret_cast<const uint16_t*>(tail + 2 * lane));
+                        if (QTYPE == 1) wv[gi].y = h2f(*reinterpret_cast<const uint16_t*>(tail + 64 + 2 * lane));
+                    }
+                    if (m_mine < p.rows) {
+                        xv[gi] = __ldg(p.xs + m_mine * p.Kg + kb);
+                        if (QTYPE == 1) gv[gi] = __ldg(p.gs + m_mine * p.Kg + kb);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i4 = 0; i4 < 4; i4++) {
+                const int r = 4 * i4 + rr;
+                const uint32_t chunk = (uint32_t)(r >> 1), sub = (uint32_t)(r & 1) * 8;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const int col = (i + (c >> 1)) & 3;  // rotated order: a half warp covers all 8 swizzle rows
-                    uint32_t lo = ww[col] & 0x0F0F0F0Fu, hi = (ww[col] >> 4) & 0x0F0F0F0Fu;
+                    const uint32_t word = col_of[i] == 0 ? w[i4].x : col_of[i] == 1 ? w[i4].y : col_of[i] == 2 ? w[i4].z : w[i4].w;
+                    uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
                     if (SIGNED) {  // sign-extend each nibble into its byte
                         lo |= (lo & 0x08080808u) * 0x1Eu;
                         hi |= (hi & 0x08080808u) * 0x1Eu;
                     }
-                    const uint32_t row = pw * 32 + 4 * c + col;
-                    const uint32_t addr = a_base + swz(row, 8 * r);
+                    const uint32_t addr = a_base + (row_off[i] & 0xFFFFu) + (((chunk ^ (row_off[i] >> 16)) & 7) << 4) + sub;
                     asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(lo), "r"(hi) : "memory");
                 }
             }
-            // ---- B: codes of row m0 + pt, 128 bytes
-            {
-                const int64_t m = m0 + pt;
-                const int8_t* src = p.codes + m * p.Kp + (int64_t)it * kStageK;
-#pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (m < p.rows && (int64_t)it * kStageK + q * 16 < p.Kp) v = __ldg(reinterpret_cast<const uint4*>(src) + q);
-                    const uint32_t addr = b_base + swz(pt, 16 * q);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
-                                 "r"(v.w)
-                                 : "memory");
-                }
-            }
-            // ---- scales of the stage's groups
 #pragma unroll
             for (int gi = 0; gi < GPS; gi++) {
-                const int kb = kb0 + gi;
-                float2 wv = make_float2(0.f, 0.f), xv = make_float2(0.f, 0.f);
-                if (kb < p.Kg) {
-                    if (stripe_live) {
-                        const uint8_t* blk = p.wq + ((int64_t)nb * p.Kg + kb) * BS + 16 * G;
-                        wv.x = h2f(*reinterpret_cast<const uint16_t*>(blk + 2 * lane));
-                        if (QTYPE == 1) wv.y = h2f(*reinterpret_cast<const uint16_t*>(blk + 64 + 2 * lane));
-                    }
-                    const int64_t m = m0 + pt;
-                    if (m < p.rows) {
-                        xv.x = __ldg(p.xs + m * p.Kg + kb);
-                        if (QTYPE == 1) xv.y = __ldg(p.gs + m * p.Kg + kb);
-                    }
-                }
-                wsc[gi * kTileN + pt] = wv;
-                xsc[gi * kTileM + pt] = xv;
+                wsc[gi * kTileN + pt] = wv[gi];
+                // row pairs are kept as {xs0, xs1, gs0, gs1} for the packed epilogue arithmetic
+                float* q = xsc + (gi * (kTileM / 2) + (pt >> 1)) * 4 + (pt & 1);
+                q[0] = xv[gi];
+                q[2] = gv[gi];
             }
             fence_proxy_async();  // generic-proxy stores above -> visible to the tensor core's async proxy
             mbar_arrive(bar_full + 8 * s);
@@ -295,19 +343,20 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
         }
         __syncwarp();
     } else {
-        // =================== epilogue: 8 warps ===================
-        const int quarter = warp & 3, half = warp >> 2;
+        // =================== epilogue: 16 warps, 32 lanes x 32 columns each ===================
+        const int quarter = warp & 3, cgrp = warp >> 2;
         const int nrow = quarter * 32 + lane;  // tile column n handled by this thread (= TMEM lane)
-        float acc[64];
+        uint64_t acc[16];                      // 32 fp32 accumulators as 16 packed pairs (rows 2j, 2j+1)
 #pragma unroll
-        for (int i = 0; i < 64; i++) acc[i] = 0.0f;
+        for (int i = 0; i < 16; i++) acc[i] = 0ull;
+        const uint64_t neg_magic = pack2(-12582912.0f, -12582912.0f);
         int gcount = 0;
         bool ok = true;
         for (int it = 0; it < nstage && ok; it++) {
             const int s = it % kStages;
             const uint8_t* st = smem + s * kStageBytes;
             const float2* wsc = reinterpret_cast<const float2*>(st + kABytes + kBBytes);
-            const float4* xsc4 = reinterpret_cast<const float4*>(st + kABytes + kBBytes + kWscBytes);
+            const ulonglong2* xsc2 = reinterpret_cast<const ulonglong2*>(st + kABytes + kBBytes + kWscBytes);
             const int ng = min(GPS, p.Kg - it * GPS);
             for (int gi = 0; gi < ng; gi++, gcount++) {
                 const int b = gcount % kTmemBufs;
@@ -316,31 +365,23 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
                     break;
                 }
                 tc_fence_after();
-                const float2 w = wsc[gi * kTileN + nrow];  // wd, wm of this thread's column
+                uint32_t v[32];
+                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kTileM + cgrp * 32, v);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * b);  // the buffer can be overwritten
+                const float2 w = wsc[gi * kTileN + nrow];          // wd, wm of this thread's column
+                const uint64_t wd2 = pack2(w.x, w.x), wm2 = pack2(w.y, w.y);
 #pragma unroll
-                for (int hh = 0; hh < 2; hh++) {  // two loads of 32 columns keep the register count down
-                    uint32_t v[32];
-                    tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kTileM + half * 64 + hh * 32, v);
-                    tc_wait_ld();
-                    if (hh == 1) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_tempty + 8 * b);  // the buffer can be overwritten
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const float4 x2 = xsc4[gi * (kTileM / 2) + half * 32 + hh * 16 + j];  // xs, gs of two rows
-                        // exact int -> float: |I| < 2^22, so (I + 0x4B400000) reinterpreted is 12582912 + I
-                        const float i0 = __int_as_float((int)v[2 * j] + 0x4B400000) - 12582912.0f;
-                        const float i1 = __int_as_float((int)v[2 * j + 1] + 0x4B400000) - 12582912.0f;
-                        const int a0 = hh * 32 + 2 * j;
-                        acc[a0] = fmaf(__fmul_rn(w.x, x2.x), i0, acc[a0]);
-                        acc[a0 + 1] = fmaf(__fmul_rn(w.x, x2.z), i1, acc[a0 + 1]);
-                        if (QTYPE == 1) {
-                            acc[a0] = fmaf(w.y, x2.y, acc[a0]);
-                            acc[a0 + 1] = fmaf(w.y, x2.w, acc[a0 + 1]);
-                        }
-                    }
+                for (int j = 0; j < 16; j++) {
+                    const ulonglong2 xg = xsc2[gi * (kTileM / 2) + cgrp * 16 + j];  // {xs0, xs1}, {gs0, gs1}
+                    // exact int -> float: |I| < 2^22, so (I + 0x4B400000) reinterpreted is 12582912 + I
+                    const uint64_t i2 = fadd2(pack2(__int_as_float((int)v[2 * j] + 0x4B400000),
+                                                    __int_as_float((int)v[2 * j + 1] + 0x4B400000)),
+                                              neg_magic);
+                    acc[j] = ffma2(fmul2(wd2, xg.x), i2, acc[j]);
+                    if (QTYPE == 1) acc[j] = ffma2(wm2, xg.y, acc[j]);
                 }
             }
             __syncwarp();
@@ -350,9 +391,12 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
             const int64_t n = n0 + nrow;
             if (n < p.N) {
 #pragma unroll
-                for (int j = 0; j < 64; j++) {
-                    const int64_t m = m0 + half * 64 + j;
-                    if (m < p.rows) p.y[m * p.ldy + n] = acc[j];
+                for (int j = 0; j < 16; j++) {
+                    const int64_t m = m0 + cgrp * 32 + 2 * j;
+                    float lo, hi;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[j]));
+                    if (m < p.rows) p.y[m * p.ldy + n] = lo;
+                    if (m + 1 < p.rows) p.y[(m + 1) * p.ldy + n] = hi;
                 }
             }
         }
@@ -368,8 +412,51 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
     }
 }
 
+// cuTensorMapEncodeTiled, looked up once through the runtime (the driver library is not linked)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+// the code matrix [rows][Kp] int8 as a 2-D tensor; boxes of 128 bytes x 128 rows land in the
+// 128-byte-swizzle layout that the MMA descriptors describe; out-of-range rows and k read as 0
+int make_codes_map(CUtensorMap* map, const int8_t* codes, int64_t rows, int64_t Kp) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+        set_error("fc_prefill: cuTensorMapEncodeTiled is not available from this driver");
+        return Q4FC_ECUDA;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)Kp};
+    const cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)kTileM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(codes), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("fc_prefill: cuTensorMapEncodeTiled failed with %d (rows=%lld, Kp=%lld)", (int)r, (long long)rows,
+                  (long long)Kp);
+        return Q4FC_ECUDA;
+    }
+    return Q4FC_OK;
+}
+
 template <int G, int QTYPE, bool SIGNED>
-int launch_prefill_variant(const PrefillParams& p, cudaStream_t s) {
+int launch_prefill_variant(const PrefillParams& p, const CUtensorMap& map, cudaStream_t s) {
     static bool attr_done[64] = {};
     int dev = 0;
     Q4FC_CUDA_OK(cudaGetDevice(&dev));
@@ -384,7 +471,7 @@ int launch_prefill_variant(const PrefillParams& p, cudaStream_t s) {
         set_error("fc_prefill: %lld x %lld tiles exceed the grid limit", (long long)n_tiles, (long long)m_tiles);
         return Q4FC_ELIMIT;
     }
-    fn<<<dim3((unsigned)n_tiles, (unsigned)m_tiles), kThreads, kSmemBytes, s>>>(p);
+    fn<<<dim3((unsigned)n_tiles, (unsigned)m_tiles), kThreads, kSmemBytes, s>>>(p, map);
     Q4FC_CUDA_OK(cudaGetLastError());
     return Q4FC_OK;
 }
@@ -432,13 +519,20 @@ int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, cons
     int rc = launch_quant_x(x, rows, K, ldx, G, 1.0f, reinterpret_cast<int8_t*>(base + l.codes),
                             reinterpret_cast<float*>(base + l.xs), reinterpret_cast<float*>(base + l.gs), s);
     if (rc) return rc;
+    if (rows > 0x7fffffffLL || p.Kp > 0x7fffffffLL) {
+        set_error("fc_prefill: rows=%lld or K=%lld beyond the 2^31 coordinate range", (long long)rows, (long long)K);
+        return Q4FC_ELIMIT;
+    }
+    CUtensorMap map;
+    rc = make_codes_map(&map, p.codes, rows, p.Kp);
+    if (rc) return rc;
     const bool sgn = (flags & Q4FC_FLAG_NIBBLE_SIGNED) && qtype == 0;
-    if (qtype == 1 && G == 32) return launch_prefill_variant<32, 1, false>(p, s);
-    if (qtype == 1 && G == 128) return launch_prefill_variant<128, 1, false>(p, s);
-    if (qtype == 0 && G == 32 && !sgn) return launch_prefill_variant<32, 0, false>(p, s);
-    if (qtype == 0 && G == 128 && !sgn) return launch_prefill_variant<128, 0, false>(p, s);
-    if (qtype == 0 && G == 32) return launch_prefill_variant<32, 0, true>(p, s);
-    return launch_prefill_variant<128, 0, true>(p, s);
+    if (qtype == 1 && G == 32) return launch_prefill_variant<32, 1, false>(p, map, s);
+    if (qtype == 1 && G == 128) return launch_prefill_variant<128, 1, false>(p, map, s);
+    if (qtype == 0 && G == 32 && !sgn) return launch_prefill_variant<32, 0, false>(p, map, s);
+    if (qtype == 0 && G == 128 && !sgn) return launch_prefill_variant<128, 0, false>(p, map, s);
+    if (qtype == 0 && G == 32) return launch_prefill_variant<32, 0, true>(p, map, s);
+    return launch_prefill_variant<128, 0, true>(p, map, s);
 }
 
 }  // namespace q4fc
