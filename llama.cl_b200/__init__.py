@@ -9,7 +9,7 @@ packed-nibble FC product, behind the reference's op names.
 
 All compute runs in ``lib/libq4fc_b200.so`` (see ``include/q4fc_b200.h``).
 """
-from . import _cabi, c_ext, llmops, ops  # noqa: F401
+from . import _cabi, c_ext, host, llmops, ops, tp  # noqa: F401
 from .llmops import fc_Q4A, offline_FC_dequant_Q4A, offline_FC_quant_Q4A  # noqa: F401
 from .ops import llmop_fc_q4a  # noqa: F401
 

@@ -91,7 +91,7 @@ class TPLinearQ4:
         key = (B, M, device)
         if key not in self._bufs:
             local = torch.zeros((B * M, self.cols), dtype=dtype, device=device)
-            gathered = torch.empty((self.world, B * M, self.cols), dtype=dtype, device=device)
+            gathered = torch.empty((self.world * B * M, self.cols), dtype=dtype, device=device)
             self._bufs[key] = (local, gathered)
         return self._bufs[key]
 
@@ -108,8 +108,8 @@ class TPLinearQ4:
             else:
                 y = self.local_fc(x, self.weight, n_local, **self.fc_kwargs)
                 local[:, :n_local].copy_(y.reshape(rows, n_local))
-        dist.all_gather_into_tensor(gathered, local, group=self.group)
-        return self.assemble(gathered, B, M)
+        dist.all_gather_into_tensor(gathered, local, group=self.group)  # rank-major concatenation along dim 0
+        return self.assemble(gathered.view(self.world, rows, self.cols), B, M)
 
     def assemble(self, gathered: torch.Tensor, B: int, M: int) -> torch.Tensor:
         """[world, rows, cols] -> [B, M, N]; a pure view when rows == 1 and N == world * cols."""
