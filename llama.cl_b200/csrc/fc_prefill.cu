@@ -22,7 +22,7 @@
 // work per (m, n, group) -- one int add, one fp add, one mul, one or two fma --
 // is what bounds this kernel: the tensor pipe waits for the epilogue.
 //
-// Warp roles (21 warps): 0-15 epilogue (warp%4 = TMEM lane quarter, warp/4 =
+// Warp roles (24 warps, 21 of them busy): 0-15 epilogue (warp%4 = TMEM lane quarter, warp/4 =
 // which 32 of the 128 tile rows), 16-19 producers (unpack A and stage the
 // scales of one 128-k stage: generic-proxy stores + fence.proxy.async; one of
 // them also issues the TMA load of the B tile from the code matrix), 20 MMA
@@ -44,7 +44,7 @@ constexpr int kStages = 4;
 constexpr int kTmemBufs = 4;
 constexpr int kEpiWarps = 16, kProdWarps = 4;
 constexpr int kProdThreads = kProdWarps * 32;
-constexpr int kThreads = (kEpiWarps + kProdWarps + 1) * 32;
+constexpr int kThreads = (kEpiWarps + kProdWarps + 4) * 32;  // the MMA warp's warpgroup is filled up with idle warps
 constexpr int kMmaWarp = kEpiWarps + kProdWarps;
 constexpr uint64_t kWaitLimitNs = 1000000000ull;  // every mbarrier wait gives up after one second
 
@@ -219,7 +219,11 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Register budget per role (whole warpgroups): the launch gives every thread 80; producers and the
+    // MMA warpgroup hand registers back, the epilogue warpgroups take 96 each (what is handed back,
+    // 4*32*16 + 4*32*56 = 9216, covers what is taken, 16*32*16 = 8192, so no request can block).
     if (warp >= kEpiWarps && warp < kMmaWarp) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         // =================== producers: one 128-k stage at a time ===================
         const int pt = threadIdx.x - kEpiWarps * 32;  // 0..127
         const int pw = pt >> 5;                       // stripe of the tile handled by this warp
@@ -309,9 +313,10 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
             fence_proxy_async();  // generic-proxy stores above -> visible to the tensor core's async proxy
             mbar_arrive(bar_full + 8 * s);
         }
-    } else if (warp == kMmaWarp) {
-        // =================== MMA issue: one elected lane ===================
-        if (lane == 0) {
+    } else if (warp >= kMmaWarp) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+        // =================== MMA issue: one elected lane of one warp ===================
+        if (warp == kMmaWarp && lane == 0) {
             // instruction descriptor: D = s32, A = u8 (s8 when sign-extended), B = s8, both K-major, N = 128, M = 128
             const uint32_t idesc = (2u << 4) | ((SIGNED ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(kTileM >> 3) << 17) |
                                    ((uint32_t)(kTileN >> 4) << 24);
@@ -343,6 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) fc_prefill_kernel(const PrefillPa
         }
         __syncwarp();
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
         // =================== epilogue: 16 warps, 32 lanes x 32 columns each ===================
         const int quarter = warp & 3, cgrp = warp >> 2;
         const int nrow = quarter * 32 + lane;  // tile column n handled by this thread (= TMEM lane)
