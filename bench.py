@@ -286,6 +286,19 @@ def our_arm(args) -> None:
     e1.record()
     barrier()
     clocks = sampler.stop()
+    if clocks["samples"] < 5:
+        # the timed region was shorter than a few NVML polls: keep replaying the same graph (untimed)
+        # for about a second and sample the clocks under that identical load
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        t_end = time.perf_counter() + 1.0
+        while time.perf_counter() < t_end:
+            for _ in range(50):
+                run_step()
+            torch.cuda.synchronize()
+        more = sampler.stop()
+        more["note"] = "sampled during an untimed one-second replay of the timed graph (timed region too short to poll)"
+        clocks = more
     ms_total = e0.elapsed_time(e1)
     if distributed:
         t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
@@ -370,15 +383,32 @@ def our_arm(args) -> None:
         gen.manual_seed(7)
         h0 = torch.randn((1, 1, H), generator=gen, device=dev, dtype=torch.float32)
 
+        side = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
+
+        def fork(fns, x_):
+            """Run independent FCs of one input side by side: the first on the current stream, the rest on side
+            streams (they become parallel branches of the captured graph); returns their outputs after the join."""
+            cur = torch.cuda.current_stream(dev)
+            start = torch.cuda.Event()
+            start.record(cur)
+            outs = [None] * len(fns)
+            for i_, f_ in enumerate(fns[1:]):
+                with torch.cuda.stream(side[i_]):
+                    side[i_].wait_event(start)
+                    outs[i_ + 1] = f_(x_)
+            outs[0] = fns[0](x_)
+            for i_ in range(len(fns) - 1):
+                cur.wait_stream(side[i_])
+            return outs
+
         def token() -> None:
+            # the seven FCs of chatllama/main.py:348-370 with their data dependences: q, k, v read the same
+            # input, as do gate and up; the non-FC ops between them are not part of this path
             h = h0
-            for f in layers:  # the seven FCs of chatllama/main.py:348-370 in call order; non-FC ops are not part of this path
-                q = f["q"](h)
-                f["k"](h)
-                f["v"](h)
+            for f in layers:
+                q, _, _ = fork([f["q"], f["k"], f["v"]], h)
                 o = f["o"](q)
-                g_ = f["gate"](o)
-                f["up"](o)
+                g_, _ = fork([f["gate"], f["up"]], o)
                 h = f["down"](g_)
             lm_head(h)
 
@@ -409,6 +439,48 @@ def our_arm(args) -> None:
         del layers, lm_head
     except Exception as e:
         stack = {"error": str(e)}
+
+    # ---- the other configurations of the path, reported beside the headline (single GPU only)
+    extras = None
+    if not distributed:
+        try:
+            extras = {}
+            gen.manual_seed(4242)
+            Wp = torch.randn((11008, 4096), generator=gen, device=dev, dtype=torch.float32) * 0.02
+
+            def timed(fn, reps):
+                fn()
+                torch.cuda.synchronize()
+                t0_, t1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0_.record()
+                for _ in range(reps):
+                    fn()
+                t1_.record()
+                torch.cuda.synchronize()
+                return t0_.elapsed_time(t1_) / reps
+
+            # prefill: Q4_0 group 32, K=4096, N=11008, M=512 and 2048 (int8 tensor-core kernel + quantizer)
+            wq0 = pkg.llmops.offline_FC_quant_Q4A(Wp, qtype="q4_0", group_k=32)
+            pre = {}
+            for M_ in (512, 2048):
+                xp = torch.randn((1, M_, 4096), generator=gen, device=dev, dtype=torch.float32)
+                yp = torch.empty((1, M_, 11008), device=dev, dtype=torch.float32)
+                wsp = pkg.llmops.fc_workspace(M_, 4096, 11008, 0, 32, dev)
+                ms_ = timed(lambda: pkg.llmops.fc_Q4A(xp, wq0, 11008, out=yp, workspace=wsp), 10)
+                wsp.check()
+                pre[f"M{M_}"] = {"ms": ms_, "tops": 2.0 * M_ * 11008 * 4096 / (ms_ * 1e-3) / 1e12}
+            extras["prefill_q4_0_g32_K4096_N11008"] = pre
+            # packer: fp32 -> Q4_1, one 11008x4096 matrix (algorithmic bytes = 4 B read + packed bytes written per weight)
+            pk = {}
+            for G_ in (32, 128):
+                outp = torch.empty(((11008 + 31) // 32, 4096 // G_, 16 * G_ + 128), dtype=torch.int8, device=dev)
+                ms_ = timed(lambda: pkg.llmops.offline_FC_quant_Q4A(Wp, qtype="q4_1", group_k=G_, out=outp), 20)
+                nbytes = Wp.numel() * 4 + outp.numel()
+                pk[f"g{G_}"] = {"ms": ms_, "gb_s": nbytes / (ms_ * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_ * 1e-3) / 1e9 / load_peaks()[0]}
+            extras["pack_q4_1_11008x4096"] = pk
+            del Wp
+        except Exception as e:
+            extras = {"error": str(e)}
 
     # ---- parity spot check of what was just timed (not timed itself)
     check = None
@@ -454,7 +526,7 @@ def our_arm(args) -> None:
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
                          "kernel": "fc_decode_cluster_kernel<128,1,false,ROWS>",
                          "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": len(calls)},
-            "cpu_baseline": cpu_baseline, "parity_spot_check": check, "fc_stack": stack,
+            "cpu_baseline": cpu_baseline, "parity_spot_check": check, "fc_stack": stack, "other_configs": extras,
         }
         _emit(json.dumps(line))
     if distributed:
