@@ -530,8 +530,13 @@ def our_arm(args) -> None:
         }
         _emit(json.dumps(line))
     if distributed:
-        dist.barrier()
-        dist.destroy_process_group()
+        # Captured graphs hold NCCL work; tearing the process group down under them has been seen to
+        # block.  Every collective of this run is behind us (the last one was the all-reduce of the
+        # timings): drain the GPU and leave without the interpreter's teardown.
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
