@@ -214,6 +214,7 @@ def our_arm(args) -> None:
     from llama_cl_b200 import tp
     from llama_cl_b200.host import HostFC
 
+    sections = set(args.sections.split(","))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -309,7 +310,7 @@ def our_arm(args) -> None:
 
     # ---- end to end: host buffers in, host buffers out, every call (eager, public API)
     e2e = None
-    if True:
+    if "e2e" in sections:
         hosts = []
         for c in calls:
             if distributed:
@@ -355,6 +356,8 @@ def our_arm(args) -> None:
     # ---- per-token pass through the FC stack of a 32-layer Llama-7B (225 FCs, batch 1)
     stack = None
     try:
+        if "stack" not in sections:
+            raise RuntimeError("section not requested")
         H, I, V, L = 4096, 11008, 32000, 32
 
         def make_fc(N, K, seed):
@@ -442,7 +445,7 @@ def our_arm(args) -> None:
 
     # ---- the other configurations of the path, reported beside the headline (single GPU only)
     extras = None
-    if not distributed:
+    if not distributed and "extras" in sections:
         try:
             extras = {}
             gen.manual_seed(4242)
@@ -502,7 +505,7 @@ def our_arm(args) -> None:
                             for c in calls)
         achieved = per_rank_algo / (ms_step * 1e-3) / 1e9
         cpu_baseline = None
-        if not distributed:
+        if not distributed and "cpu" in sections:
             try:
                 work, run, kind, cores = cpu_sweep_setup(SHAPES, MS)
                 t_probe = time_cpu_sweep(work, run, 1, 1)
@@ -552,6 +555,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sections", default="e2e,stack,extras,cpu",
+                    help="optional legs beside the timed sweep (a profiler run asks for none of them: --sections none)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
