@@ -169,8 +169,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) fc_decode_kernel(const DecodeP
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, SEG));
                 fsum += __shfl_xor_sync(0xffffffffu, fsum, off, SEG);
             }
-            const float d = __fdiv_rn(amax, 127.0f);
-            const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+            const float d = div_const_rn(amax, 127.0f, 1.0f / 127.0f);
+            const float id = inv_or_zero(d);
             uint32_t packed = 0;
             int isum = 0;
 #pragma unroll

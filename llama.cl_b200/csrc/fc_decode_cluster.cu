@@ -87,7 +87,7 @@ struct ClusterParams {
 
 __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-    asm volatile(
+    asm(  // a pure function of its operands: left to the scheduler to interleave
         "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -247,8 +247,8 @@ __global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const C
             }
 #pragma unroll
             for (int m = 0; m < ROWS; m++) {
-                const float d = __fdiv_rn(amax[m], 127.0f);
-                const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+                const float d = div_const_rn(amax[m], 127.0f, 1.0f / 127.0f);
+                const float id = inv_or_zero(d);
                 uint32_t packed = 0;
                 int isum = 0;
 #pragma unroll
@@ -317,7 +317,8 @@ __global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const C
 #pragma unroll
         for (int i = 0; i < NBLK; i++) {
             if (f + i < f1) {
-                int ia[4] = {0, 0, 0, 0}, ib[4] = {0, 0, 0, 0};
+                // two accumulator chains per tile (even / odd row sets) halve the dependent-MMA latency
+                int ia[4] = {0, 0, 0, 0}, ib[4] = {0, 0, 0, 0}, ja[4] = {0, 0, 0, 0}, jb[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int jj = 0; jj < SETS; jj++) {
                     uint2 xb = make_uint2(0u, 0u);
@@ -330,9 +331,16 @@ __global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const C
                         l0 ^= 0x08080808u, l1 ^= 0x08080808u, l2 ^= 0x08080808u, l3 ^= 0x08080808u;
                         h0 ^= 0x08080808u, h1 ^= 0x08080808u, h2 ^= 0x08080808u, h3 ^= 0x08080808u;
                     }
-                    mma_u8s8(ia, l0, l1, h0, h1, xb.x, xb.y);
-                    mma_u8s8(ib, l2, l3, h2, h3, xb.x, xb.y);
+                    if (jj & 1) {
+                        mma_u8s8(ja, l0, l1, h0, h1, xb.x, xb.y);
+                        mma_u8s8(jb, l2, l3, h2, h3, xb.x, xb.y);
+                    } else {
+                        mma_u8s8(ia, l0, l1, h0, h1, xb.x, xb.y);
+                        mma_u8s8(ib, l2, l3, h2, h3, xb.x, xb.y);
+                    }
                 }
+#pragma unroll
+                for (int q = 0; q < 4; q++) ia[q] += ja[q], ib[q] += jb[q];
                 const float4 s4 = *reinterpret_cast<const float4*>(sc + ck * 16 + t * 4);  // xs0, gs0, xs1, gs1
                 const float2 wd01 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].x));
                 const float2 wd23 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].y));

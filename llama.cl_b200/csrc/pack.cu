@@ -122,13 +122,13 @@ __global__ void __launch_bounds__(kPackThreads) pack_kernel(const float* __restr
 
         float d, m, id;
         if (QTYPE == 1) {
-            d = __fdiv_rn(vmax - vmin, 15.0f);
+            d = div_const_rn(__fsub_rn(vmax, vmin), 15.0f, 1.0f / 15.0f);
             m = vmin;
         } else {
-            d = __fdiv_rn(fmaxf(fabsf(vmin), fabsf(vmax)), 7.0f);
+            d = div_const_rn(fmaxf(fabsf(vmin), fabsf(vmax)), 7.0f, 1.0f / 7.0f);
             m = 0.0f;
         }
-        id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+        id = inv_or_zero(d);
 
         uint32_t word = 0;
         if (cnt >= 0) {

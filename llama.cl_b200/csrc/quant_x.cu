@@ -68,8 +68,8 @@ __global__ void __launch_bounds__(kQxWarps * 32) quant_x_kernel(const float* __r
 #pragma unroll
     for (int off = SEG / 2; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, SEG));
 
-    const float d = __fdiv_rn(amax, 127.0f);
-    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    const float d = div_const_rn(amax, 127.0f, 1.0f / 127.0f);
+    const float id = inv_or_zero(d);
 
     uint32_t packed = 0;
 #pragma unroll
