@@ -100,25 +100,39 @@ __global__ void __launch_bounds__(kPackThreads) pack_kernel(const float* __restr
         const int n_l = (u % (32 / NPW)) * NPW + lane / SEG;
         const int cnt = nvalid[it];
 
-        MinMax mm;
-        mm.has = cnt > 0;
-        mm.vmin = mm.vmax = v[it][0];
+        // Fast path (whole warp has 8 valid values per lane): plain min / max and an xor butterfly.
+        // The value of a minimum / maximum does not depend on the scan order; only the SIGN of a zero
+        // does (get_min_max keeps the first of equal values), so when any lane of the warp ends up with
+        // a zero minimum or maximum, or values are missing, the warp redoes the reduction in order.
+        float vmin = v[it][0], vmax = v[it][0];
 #pragma unroll
-        for (int j = 1; j < 8; j++)
-            if (j < cnt) mm_take(mm, v[it][j]);
-        // ordered segmented reduction: lane i absorbs lane i+off (later k)
+        for (int j = 1; j < 8; j++) vmin = fminf(vmin, v[it][j]), vmax = fmaxf(vmax, v[it][j]);
 #pragma unroll
         for (int off = 1; off < SEG; off <<= 1) {
-            float rmin = __shfl_down_sync(0xffffffffu, mm.vmin, off, SEG);
-            float rmax = __shfl_down_sync(0xffffffffu, mm.vmax, off, SEG);
-            int rhas = __shfl_down_sync(0xffffffffu, mm.has, off, SEG);
-            if (seg_lane + off < SEG && rhas) {
-                if (mm.vmax < rmax) mm.vmax = rmax;
-                if (mm.vmin > rmin) mm.vmin = rmin;
-            }
+            vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, off));
+            vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
         }
-        const float vmin = __shfl_sync(0xffffffffu, mm.vmin, 0, SEG);
-        const float vmax = __shfl_sync(0xffffffffu, mm.vmax, 0, SEG);
+        if (__any_sync(0xffffffffu, cnt != 8 || vmin == 0.0f || vmax == 0.0f)) {
+            MinMax mm;
+            mm.has = cnt > 0;
+            mm.vmin = mm.vmax = v[it][0];
+#pragma unroll
+            for (int j = 1; j < 8; j++)
+                if (j < cnt) mm_take(mm, v[it][j]);
+            // ordered segmented reduction: lane i absorbs lane i+off (later k)
+#pragma unroll
+            for (int off = 1; off < SEG; off <<= 1) {
+                float rmin = __shfl_down_sync(0xffffffffu, mm.vmin, off, SEG);
+                float rmax = __shfl_down_sync(0xffffffffu, mm.vmax, off, SEG);
+                int rhas = __shfl_down_sync(0xffffffffu, mm.has, off, SEG);
+                if (seg_lane + off < SEG && rhas) {
+                    if (mm.vmax < rmax) mm.vmax = rmax;
+                    if (mm.vmin > rmin) mm.vmin = rmin;
+                }
+            }
+            vmin = __shfl_sync(0xffffffffu, mm.vmin, 0, SEG);
+            vmax = __shfl_sync(0xffffffffu, mm.vmax, 0, SEG);
+        }
 
         float d, m, id;
         if (QTYPE == 1) {
@@ -134,14 +148,19 @@ __global__ void __launch_bounds__(kPackThreads) pack_kernel(const float* __restr
         if (cnt >= 0) {
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-                int q = 0;
                 if (j < cnt) {
-                    const float t = __fmul_rn(__fsub_rn(v[it][j], m), id);
-                    q = round_half_away(t);
-                    q = (QTYPE == 1) ? min(15, max(q, 0)) : min(7, max(q, -7));
+                    // byte (j&3), low nibble for j<4, high nibble for j>=4 (ops/op_fc.hpp:39-48)
+                    const uint32_t place = 1u << (8 * (j & 3) + 4 * (j >> 2));
+                    if (QTYPE == 1) {
+                        // (w - m) * id >= 0: roundf is trunc(t + 0.5) with the add rounded toward zero; clamp at 15
+                        const float t = __fmul_rn(__fsub_rn(v[it][j], m), id);
+                        const uint32_t q = (uint32_t)min(15, __float2int_rz(__fadd_rz(t, 0.5f)));
+                        word += q * place;  // nibbles do not overlap: a multiply-add places the code
+                    } else {
+                        const int q = min(7, max(round_half_away(__fmul_rn(v[it][j], id)), -7));
+                        word += (uint32_t)(q & 0xF) * place;
+                    }
                 }
-                // byte (j&3), low nibble for j<4, high nibble for j>=4 (ops/op_fc.hpp:39-48)
-                word |= (uint32_t)(q & 0xF) << (8 * (j & 3) + 4 * (j >> 2));
             }
         }
         stage[kb_l * (BS / 4) + seg_lane * 32 + n_l] = word;
