@@ -13,13 +13,19 @@ per step, four times the L2), so no call finds its weights in cache.  Weights
 
 value  packed weight GB/s (packed bytes / time, 1 GB = 1e9 B: the reference's
        own "Bound: GB/s" figure of ops/perf_ops.py:243-245), inputs resident
-       in HBM, the 16 calls of a step replayed as one CUDA graph.
-e2e    the same metric through the host-buffer API: activations copied from
-       pinned host memory, result copied back, every call.
+       in HBM, the 16 calls of a step replayed as one CUDA graph.  The calls
+       are independent, so the graph runs them on --lanes parallel branches
+       (default 4); the roofline figure is taken from a second timed pass with
+       the same launches strictly one after the other.
+e2e    the same metric through the host-buffer API (HostFC): activations
+       copied from pinned host memory, result copied back, every call.
 
-With --gpus N > 1 every FC weight is split along N over the ranks and the
-outputs are joined by an all-gather (strong scaling: the job is the same
-sweep, each rank streams 1/N of every weight).
+With --gpus N > 1 every FC weight is split along N over the ranks (strong
+scaling: the job is the same sweep, each rank streams 1/N of every weight).
+--tp fused (default): the FC kernel stores its columns, stamped with the
+step number, into every rank's output buffer over NVLink; consumers wait
+word by word for the current stamp.
+--tp nccl: the slices are joined by an NCCL all-gather after every FC.
 
 --impl reference times the reference's own CPU FC (compiled from its sources
 into oracle/_ref when that was possible, else the C restatement in oracle/)
@@ -228,6 +234,29 @@ def our_arm(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     pkg._cabi.lib()
 
+    # ---- how the ranks' column slices meet
+    arena, tp_mode, tp_note = None, ("none" if not distributed else args.tp), None
+    if distributed and tp_mode == "fused":
+        try:
+            arena = tp.TPArena(128 << 20, dev)
+        except Exception as e:  # no peer mapping on this box: the collective-library form still works
+            tp_note = f"peer-mapped arena unavailable ({e}); joined by NCCL all-gather instead"
+            print(f"[bench] {tp_note}", file=sys.stderr)
+            tp_mode = "nccl"
+        flag = torch.tensor([1 if tp_mode == "fused" else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # all ranks take the same route
+        if int(flag.item()) == 0 and tp_mode == "fused":
+            tp_mode, tp_note = "nccl", "another rank could not map the arena; joined by NCCL all-gather instead"
+    fused = tp_mode == "fused"
+    # a schedule is a set of FCs that always run together: the sweep is one, the token pass another,
+    # and each call of the host-buffer leg stands alone
+    sweep_sched = tp.TPSchedule(arena) if fused else None
+
+    def make_layer(sched, wq_, N_, max_rows=8):
+        if fused:
+            return tp.FusedTPLinearQ4(sched, wq_, N_, max_rows=max_rows, pdl=True)
+        return tp.TPLinearQ4(wq_, N_, pdl=True, workspace=ws, path="decode")
+
     # ---- inputs: one packed weight per (shape, M); with TP each rank packs only its rows
     ws = pkg.llmops.fc_workspace(8, 11008, 32000, QTYPE, GROUP_K, dev)
     gen = torch.Generator(device=dev)
@@ -240,17 +269,58 @@ def our_arm(args) -> None:
             wq = pkg.llmops.offline_FC_quant_Q4A(W[n0:n1].contiguous(), qtype="q4_1", group_k=GROUP_K)
             del W
             x = torch.randn((1, M, K), generator=gen, device=dev, dtype=torch.float32)
-            layer = tp.TPLinearQ4(wq, N, pdl=True, workspace=ws, path="decode") if distributed else None
+            layer = make_layer(sweep_sched, wq, N) if distributed else None
             calls.append({"x": x, "wq": wq, "N": N, "n_local": n1 - n0, "M": M, "K": K, "layer": layer,
+                          "y_full": torch.empty((1, M, N), device=dev, dtype=torch.float32) if fused else None,
                           "y": torch.empty((1, M, n1 - n0), device=dev, dtype=torch.float32)})
     torch.cuda.synchronize()
 
-    def step_device() -> None:
-        for c in calls:
-            if distributed:
+    # The 16 calls of a step are independent of one another, so a step may run them side by side: they are
+    # dealt over `lanes` streams (longest first, each to the least loaded lane) that become parallel
+    # branches of the step's CUDA graph.  While one call is in its short latency-bound phases (activation
+    # quantization, the cluster reduction) the others keep HBM busy.  lanes = 1 is the plain one-after-the-
+    # other order, timed as well: the per-launch roofline figure comes from that pass.
+    n_lanes = 1 if tp_mode == "nccl" else max(1, args.lanes)  # one communicator: its collectives stay in order
+    lane_streams = [torch.cuda.Stream(dev) for _ in range(n_lanes)]
+
+    def deal(n: int):
+        load, plan = [0.0] * n, [[] for _ in range(n)]
+        for c in sorted(calls, key=lambda c: -packed_bytes(c["K"], c["n_local"])):
+            i = load.index(min(load))
+            plan[i].append(c)
+            load[i] += packed_bytes(c["K"], c["n_local"]) / 5e12 + 4e-6 * (1 + c["M"] / 8)
+        return plan
+
+    def run_calls(cs, pdl: bool = True) -> None:
+        outs = []
+        for c in cs:
+            if fused:
+                outs.append((c, c["layer"](c["x"])))
+            elif distributed:
                 c["layer"](c["x"])
             else:
-                pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=ws, pdl=True, path="decode")
+                pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=ws, pdl=pdl, path="decode")
+        # fused: unpack to plain fp32 behind the lane's FCs (each unpacking kernel waits for the other ranks'
+        # columns), so that the step ends when every rank holds every full output
+        for c, o in outs:
+            o.tensor(out=c["y_full"])
+
+    def step_device(lanes: int = n_lanes) -> None:
+        cur = torch.cuda.current_stream(dev)
+        if fused:
+            sweep_sched.step_begin()
+        if lanes == 1:
+            # plain launches, each after the one before has finished: nothing of one launch hides in another
+            run_calls(calls, pdl=distributed or n_lanes == 1)
+            return
+        start = torch.cuda.Event()
+        start.record(cur)
+        for st, cs in zip(lane_streams, deal(lanes)):
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                run_calls(cs)
+        for st in lane_streams[:lanes]:
+            cur.wait_stream(st)
 
     def capture(fn):
         """Two eager runs (kernel attributes, TP buffers), then one CUDA graph of fn; fn itself if capture fails."""
@@ -308,27 +378,61 @@ def our_arm(args) -> None:
     ms_step = ms_total / args.steps
     value = STEP_WEIGHT_BYTES / (ms_step * 1e-3) / 1e9
 
+    # ---- the same 16 launches one after the other on one stream: the per-launch figure of the roofline
+    ms_serial, serial_graphed = ms_step, graphed
+    if n_lanes > 1:
+        run_serial, serial_graphed = capture(lambda: step_device(1))
+        n_serial = max(3, min(args.steps, 500))
+        for _ in range(3):
+            run_serial()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(n_serial):
+            run_serial()
+        s1.record()
+        barrier()
+        ms_serial = s0.elapsed_time(s1)
+        if distributed:
+            t = torch.tensor([ms_serial], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_serial = float(t.item())
+        ms_serial /= n_serial
+
     # ---- end to end: host buffers in, host buffers out, every call (eager, public API)
     e2e = None
     if "e2e" in sections:
         hosts = []
         for c in calls:
-            if distributed:
+            if fused:
+                hosts.append(make_layer(tp.TPSchedule(arena), c["wq"], c["N"]))  # each call stands alone
+            elif distributed:
                 hosts.append(None)
             else:
-                hosts.append(HostFC(c["wq"], c["N"], max_rows=8, workspace=ws, path="decode"))
-        xs_host = [c["x"].cpu().pin_memory() for c in calls]
+                hosts.append(HostFC(c["wq"], c["N"], max_rows=8, workspace=ws, path="decode",
+                                    stream=lane_streams[len(hosts) % n_lanes]))
+        # single GPU: the activations sit in the pinned input buffer of the call's HostFC
+        xs_host = [c["x"].cpu().pin_memory() if distributed else h.x_staging(c["M"]).copy_(c["x"].cpu())
+                   for c, h in zip(calls, hosts)]
         ys_host = [torch.empty((1, c["M"], c["N"]), dtype=torch.float32).pin_memory() for c in calls]
 
         def step_e2e() -> None:
             for c, h, xh, yh in zip(calls, hosts, xs_host, ys_host):
-                if distributed:
+                if fused:
+                    c["x"].copy_(xh, non_blocking=True)
+                    h.schedule.step_begin()
+                    yh.copy_(h(c["x"]).tensor(out=c["y_full"]), non_blocking=True)
+                elif distributed:
                     c["x"].copy_(xh, non_blocking=True)
                     y = c["layer"](c["x"])
                     yh.copy_(y, non_blocking=True)
                 else:
                     h(xh, sync=False)
-            torch.cuda.current_stream(dev).synchronize()
+            if distributed:
+                torch.cuda.current_stream(dev).synchronize()
+            else:
+                for st in lane_streams:
+                    st.synchronize()
 
         n_e2e = max(3, min(args.steps, 200))
         for _ in range(3):
@@ -361,18 +465,21 @@ def our_arm(args) -> None:
         H, I, V, L = 4096, 11008, 32000, 32
 
         def make_fc(N, K, seed):
+            """-> (fn(x) -> y, packed bytes on this rank)"""
             gen.manual_seed(seed)
             n0, n1 = tp.shard_rows(N, world, rank) if distributed else (0, N)
             Wf = torch.randn((N, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
             wq_ = pkg.llmops.offline_FC_quant_Q4A(Wf[n0:n1].contiguous(), qtype="q4_1", group_k=GROUP_K)
             del Wf
+            if fused:
+                return make_layer(tok_sched, wq_, N, max_rows=1), wq_.numel()
             if distributed:
-                lay = tp.TPLinearQ4(wq_, N, pdl=True, workspace=ws, path="decode")
-                return lay, wq_.numel()
+                return make_layer(None, wq_, N), wq_.numel()
             out = torch.empty((1, 1, N), device=dev, dtype=torch.float32)
             return (lambda x_, wq_=wq_, N=N, out=out: pkg.llmops.fc_Q4A(
                 x_, wq_, N, out=out, workspace=ws, pdl=True, path="decode")), wq_.numel()
 
+        tok_sched = tp.TPSchedule(arena) if fused else None
         layers, stack_bytes_rank = [], 0
         for li in range(L):
             fcs = {}
@@ -382,6 +489,7 @@ def our_arm(args) -> None:
                 stack_bytes_rank += nb
             layers.append(fcs)
         lm_head, nb = make_fc(V, H, 49999)
+        logits = torch.empty((1, 1, V), device=dev, dtype=torch.float32)
         stack_bytes_rank += nb
         gen.manual_seed(7)
         h0 = torch.randn((1, 1, H), generator=gen, device=dev, dtype=torch.float32)
@@ -408,12 +516,16 @@ def our_arm(args) -> None:
             # the seven FCs of chatllama/main.py:348-370 with their data dependences: q, k, v read the same
             # input, as do gate and up; the non-FC ops between them are not part of this path
             h = h0
+            if fused:
+                tok_sched.step_begin()
             for f in layers:
                 q, _, _ = fork([f["q"], f["k"], f["v"]], h)
                 o = f["o"](q)
                 g_, _ = fork([f["gate"], f["up"]], o)
                 h = f["down"](g_)
-            lm_head(h)
+            y = lm_head(h)
+            if fused:
+                y.tensor(out=logits)  # the token is done when every rank holds the whole logits row
 
         run_token, tok_graphed = capture(token)
         n_tok = max(3, min(args.steps, 100))
@@ -487,6 +599,19 @@ def our_arm(args) -> None:
 
     # ---- parity spot check of what was just timed (not timed itself)
     check = None
+    y_tp = None
+    if distributed:
+        # one more untimed step; every rank must now hold the same full output of the first call
+        c = calls[0]
+        if fused:
+            step_device()
+            y_tp = c["y_full"].reshape(c["M"], c["N"]).clone()
+        else:
+            y_tp = c["layer"](c["x"]).reshape(c["M"], c["N"]).clone()
+        lo, hi = y_tp.clone(), y_tp.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        ranks_agree = bool(torch.equal(lo, hi))
     if rank == 0:
         import numpy as np
 
@@ -497,13 +622,19 @@ def our_arm(args) -> None:
             y = pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], workspace=ws).cpu().numpy()
             want = cpu.restated.fc(c["x"].cpu().numpy(), c["wq"].cpu().numpy(), c["N"])
             check = bool(np.allclose(y, want, rtol=1e-3, atol=1e-4))
+        else:
+            # this rank's own columns against the CPU restatement of its shard, and all ranks bit-equal
+            want = cpu.restated.fc(c["x"].cpu().numpy(), c["wq"].cpu().numpy(), c["n_local"])
+            mine = y_tp[:, : c["n_local"]].cpu().numpy().reshape(want.shape)
+            check = bool(np.allclose(mine, want, rtol=1e-3, atol=1e-4)) and ranks_agree
 
+    tp_status = arena.status() if fused else 0  # non-zero: a bounded wait on another rank ran out
     if rank == 0:
         peak, peak_kind = load_peaks()
         # per launch: the step's algorithmic bytes and time divided by its 16 launches
         per_rank_algo = sum(packed_bytes(c["K"], c["n_local"]) + 4 * c["M"] * c["K"] + 4 * c["M"] * c["n_local"]
                             for c in calls)
-        achieved = per_rank_algo / (ms_step * 1e-3) / 1e9
+        achieved = per_rank_algo / (ms_serial * 1e-3) / 1e9
         cpu_baseline = None
         if not distributed and "cpu" in sections:
             try:
@@ -522,13 +653,24 @@ def our_arm(args) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
             "dtype": "int8xuint4->int32, fp32 scaling", "data": "synthetic",
-            "config": dict(CONFIG, parallelism=("single GPU" if world == 1 else f"N-split tp{world} + all-gather"),
-                           launch=("cuda graph of one step" if graphed else "eager")),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": len(calls) * args.steps,
+            "config": dict(CONFIG, parallelism=(
+                "single GPU" if world == 1 else
+                f"N-split tp{world}, columns stored into every rank's buffer by the FC kernel (epoch-stamped 64-bit "
+                f"words, NVLink peer stores)" if fused else f"N-split tp{world} + NCCL all-gather"),
+                           **({"tp_note": tp_note} if tp_note else {}),
+                           launch=(f"cuda graph of one step, the 16 independent calls on {n_lanes} parallel branches"
+                                   if graphed else "eager"),
+                           lanes=n_lanes),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": (len(calls) * (2 if fused else 1) + (1 if fused else 0)) * args.steps,
+            **({"tp_status": tp_status} if fused else {}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
                          "kernel": "fc_decode_cluster_kernel<128,1,false,ROWS>",
-                         "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": len(calls)},
+                         "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": len(calls),
+                         "timed_as": "the 16 launches one after the other on one stream, plain stream order (a "
+                                     "second timed pass); average launch duration = pass time / 16",
+                         "ms_per_step_serial": ms_serial,
+                         "value_serial": STEP_WEIGHT_BYTES / (ms_serial * 1e-3) / 1e9},
             "cpu_baseline": cpu_baseline, "parity_spot_check": check, "fc_stack": stack, "other_configs": extras,
         }
         _emit(json.dumps(line))
@@ -555,6 +697,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--lanes", type=int, default=4,
+                    help="parallel graph branches the 16 independent calls of a step are dealt over (1: in order)")
+    ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
+                    help="with --gpus N > 1: how the ranks' output columns meet")
     ap.add_argument("--sections", default="e2e,stack,extras,cpu",
                     help="optional legs beside the timed sweep (a profiler run asks for none of them: --sections none)")
     args = ap.parse_args()

@@ -140,6 +140,60 @@ int q4fc_fc_decode_noalloc(const float* x, int64_t rows, int64_t K, int64_t ldx,
                            int64_t Kg, int qtype, int group_k, int64_t N, float* y, int64_t ldy, unsigned flags,
                            q4fc_stream_t stream);
 
+/* ---- one FC split along N over the GPUs of a node, joined inside the kernel ----
+ * No counterpart in the reference (it has no multi-device code).  Each rank
+ * holds the contiguous stripe range [nb0, nb1) of the packed tensor.  Outputs
+ * travel as 8-byte "stamped" words: the fp32 value in the low half, the low 32
+ * bits of a step counter (the "epoch") in the high half.  The decode kernel
+ * stores its columns, stamped, straight into the output buffer of EVERY rank
+ * (peer-mapped pointers, plain 64-bit stores over NVLink).  A 64-bit store is
+ * indivisible, so a reader that finds the current epoch in a word has its value
+ * too: no fence, no flag, no collective call, no extra launch.  An FC whose
+ * input is such a buffer (x_stamped) re-reads each word until its stamp is the
+ * current epoch (bounded: after one second *status becomes non-zero and the
+ * kernel carries on; once it is non-zero later waits end at once).
+ *
+ * The shared memory comes from an "arena": cudaMalloc'ed and zeroed by
+ * q4fc_tp_arena_create, exported as a 64-byte CUDA IPC handle that the host
+ * ships to the other ranks by any transport, and mapped there with
+ * q4fc_tp_arena_open (peer access over NVLink).  Every rank lays its arena out
+ * identically, so a peer's pointer is its mapped base plus the local offset.
+ *
+ * An epoch belongs to a "schedule": a fixed set of FC calls that run together,
+ * each exactly once per step.  Per step each rank calls q4fc_tp_step_begin once
+ * before the schedule's first FC: it adds 1 to the local epoch and is a barrier
+ * over the ranks (bounded the same way), so nobody overwrites a buffer that a
+ * slower rank is still reading from the step before.  Independent work gets
+ * its own epoch and barrier words.  q4fc_tp_collect unpacks a stamped buffer
+ * into plain floats, waiting for every word -- the hand-over to consumers that
+ * are not FC kernels.  All of it can be captured in a CUDA graph: the epoch
+ * lives in device memory. */
+typedef struct q4fc_tp_site {
+    int world;                       /* ranks, 1..8 */
+    int x_stamped;                   /* x is a stamped buffer of this rank (ldx counts 8-byte words) */
+    int64_t col_off;                 /* first output column of this rank's slice: 32 * nb0 */
+    unsigned long long* y_peer[8];   /* every rank's stamped output [rows, ldy], own rank included */
+    const unsigned long long* epoch; /* local step counter, advanced by q4fc_tp_step_begin */
+    int* status;                     /* local int, set non-zero when a bounded wait ran out */
+} q4fc_tp_site;
+
+int q4fc_tp_arena_create(size_t bytes, void** base, void* ipc_handle_64);
+int q4fc_tp_arena_open(const void* ipc_handle_64, void** peer_base);
+int q4fc_tp_arena_close(void* peer_base);
+int q4fc_tp_arena_destroy(void* base);
+/* barrier_peer[r]: rank r's barrier counter (own rank included), barrier_local: this rank's. */
+int q4fc_tp_step_begin(unsigned long long* epoch, unsigned long long* const* barrier_peer,
+                       const unsigned long long* barrier_local, int world, int* status, q4fc_stream_t stream);
+/* stamped [rows, ld] (this rank's buffer) -> dst fp32 [rows, ldd], columns [0, N). */
+int q4fc_tp_collect(const unsigned long long* stamped, int64_t rows, int64_t N, int64_t ld, float* dst, int64_t ldd,
+                    const unsigned long long* epoch, int* status, q4fc_stream_t stream);
+/* x: fp32 [rows, ldx], or with site->x_stamped a stamped buffer passed through the same pointer.
+ * N, Ng: this rank's slice (N = 32 * Ng except on the rank holding the ragged tail); ldy: row pitch of the
+ * stamped output in words.  rows <= 8.  flags as q4fc_fc_decode (Q4FC_FLAG_STREAMK is not accepted). */
+int q4fc_fc_decode_tp(const void* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                      int qtype, int group_k, int64_t N, int64_t ldy, const q4fc_tp_site* site, unsigned flags,
+                      q4fc_stream_t stream);
+
 /* Reads and clears the device status word kept at the start of a workspace
  * (host-synchronous: waits for `stream`).  Returns Q4FC_OK or Q4FC_EDEVICE. */
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream);

@@ -21,7 +21,21 @@ SYMBOLS = (
     "q4fc_version", "q4fc_strerror", "q4fc_last_error", "q4fc_block_bytes", "q4fc_infer_variant",
     "q4fc_pack", "q4fc_dequant", "q4fc_quant_x", "q4fc_fc_workspace_bytes", "q4fc_fc_workspace_init",
     "q4fc_fc_decode", "q4fc_fc_prefill", "q4fc_fc", "q4fc_fc_check_status", "q4fc_fc_decode_noalloc",
+    "q4fc_tp_arena_create", "q4fc_tp_arena_open", "q4fc_tp_arena_close", "q4fc_tp_arena_destroy",
+    "q4fc_tp_step_begin", "q4fc_tp_collect", "q4fc_fc_decode_tp",
 )
+
+
+class TpSite(C.Structure):
+    """``q4fc_tp_site`` of include/q4fc_b200.h."""
+    _fields_ = [
+        ("world", C.c_int),
+        ("x_stamped", C.c_int),
+        ("col_off", C.c_int64),
+        ("y_peer", C.c_void_p * 8),
+        ("epoch", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
 
 _lib = None
 
@@ -53,6 +67,13 @@ def lib() -> C.CDLL:
         getattr(L, name).argtypes = fc_args
     L.q4fc_fc_check_status.argtypes = [vp, vp]
     L.q4fc_fc_decode_noalloc.argtypes = [vp, i64, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, u32, vp]
+    L.q4fc_tp_arena_create.argtypes = [sz, C.POINTER(vp), C.c_char_p]
+    L.q4fc_tp_arena_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    L.q4fc_tp_arena_close.argtypes = [vp]
+    L.q4fc_tp_arena_destroy.argtypes = [vp]
+    L.q4fc_tp_step_begin.argtypes = [vp, C.POINTER(vp), vp, i32, vp, vp]
+    L.q4fc_tp_collect.argtypes = [vp, i64, i64, i64, vp, i64, vp, vp, vp]
+    L.q4fc_fc_decode_tp.argtypes = [vp, i64, i64, i64, vp, i64, i64, i32, i32, i64, i64, C.POINTER(TpSite), u32, vp]
     _lib = L
     return L
 

@@ -262,6 +262,108 @@ int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq
     return q4fc_fc_prefill(x, rows, K, ldx, wq, Ng, Kg, qtype, group_k, N, y, ldy, ws, ws_bytes, flags, stream);
 }
 
+int q4fc_tp_arena_create(size_t bytes, void** base, void* ipc_handle_64) {
+    if (!base || !ipc_handle_64 || bytes == 0) {
+        set_error("tp_arena_create: null argument or zero size");
+        return Q4FC_EINVAL;
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the IPC handle is shipped as 64 bytes");
+    void* p = nullptr;
+    Q4FC_CUDA_OK(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(e, "tp_arena_create");
+    }
+    memcpy(ipc_handle_64, &h, sizeof(h));
+    *base = p;
+    return Q4FC_OK;
+}
+
+int q4fc_tp_arena_open(const void* ipc_handle_64, void** peer_base) {
+    if (!ipc_handle_64 || !peer_base) {
+        set_error("tp_arena_open: null argument");
+        return Q4FC_EINVAL;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, ipc_handle_64, sizeof(h));
+    Q4FC_CUDA_OK(cudaIpcOpenMemHandle(peer_base, h, cudaIpcMemLazyEnablePeerAccess));
+    return Q4FC_OK;
+}
+
+int q4fc_tp_arena_close(void* peer_base) {
+    if (peer_base) Q4FC_CUDA_OK(cudaIpcCloseMemHandle(peer_base));
+    return Q4FC_OK;
+}
+
+int q4fc_tp_arena_destroy(void* base) {
+    if (base) Q4FC_CUDA_OK(cudaFree(base));
+    return Q4FC_OK;
+}
+
+int q4fc_tp_step_begin(unsigned long long* epoch, unsigned long long* const* barrier_peer,
+                       const unsigned long long* barrier_local, int world, int* status, q4fc_stream_t stream) {
+    if (!epoch || !barrier_peer || !barrier_local || !status || world < 1 || world > 8) {
+        set_error("tp_step_begin: null argument or world=%d outside 1..8", world);
+        return Q4FC_EINVAL;
+    }
+    for (int i = 0; i < world; i++)
+        if (!barrier_peer[i] || !aligned(barrier_peer[i], 8)) {
+            set_error("tp_step_begin: barrier_peer[%d] is null or misaligned", i);
+            return Q4FC_EINVAL;
+        }
+    return launch_tp_step_begin(epoch, barrier_peer, barrier_local, world, status, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_tp_collect(const unsigned long long* stamped, int64_t rows, int64_t N, int64_t ld, float* dst, int64_t ldd,
+                    const unsigned long long* epoch, int* status, q4fc_stream_t stream) {
+    if (!stamped || !dst || !epoch || !status || rows < 0 || N < 0 || ld < N || ldd < N || !aligned(stamped, 8)) {
+        set_error("tp_collect: null or misaligned pointer, negative size, or pitch smaller than N");
+        return Q4FC_EINVAL;
+    }
+    return launch_tp_collect(stamped, rows, N, ld, dst, ldd, epoch, status, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_fc_decode_tp(const void* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                      int qtype, int group_k, int64_t N, int64_t ldy, const q4fc_tp_site* site, unsigned flags,
+                      q4fc_stream_t stream) {
+    if (!site || site->world < 1 || site->world > 8 || !site->epoch || !site->status) {
+        set_error("fc_decode_tp: null site, or world outside 1..8, or null epoch/status");
+        return Q4FC_EINVAL;
+    }
+    if (flags & Q4FC_FLAG_STREAMK) {
+        set_error("fc_decode_tp: Q4FC_FLAG_STREAMK is not available for the multi-GPU form");
+        return Q4FC_EINVAL;
+    }
+    if (site->col_off < 0 || site->col_off % 32 != 0 || site->col_off + N > ldy) {
+        set_error("fc_decode_tp: col_off=%lld must be a multiple of 32 with col_off + N <= ldy",
+                  (long long)site->col_off);
+        return Q4FC_EINVAL;
+    }
+    for (int i = 0; i < site->world; i++)
+        if (!site->y_peer[i] || !aligned(site->y_peer[i], 8)) {
+            set_error("fc_decode_tp: y_peer[%d] is null or not 8-byte aligned", i);
+            return Q4FC_EINVAL;
+        }
+    if (site->x_stamped && !aligned(x, 8)) {
+        set_error("fc_decode_tp: a stamped x needs 8-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    if (int rc = check_fc_args("fc_decode_tp", static_cast<const float*>(x), rows, K, ldx, wq, Ng, Kg, qtype, group_k,
+                               N, reinterpret_cast<float*>(site->y_peer[0]), ldy))
+        return rc;
+    if (rows > kMaxDecodeRows) {
+        set_error("fc_decode_tp: rows=%lld exceeds %d", (long long)rows, kMaxDecodeRows);
+        return Q4FC_ELIMIT;
+    }
+    return launch_fc_decode_cluster_tp(static_cast<const float*>(x), (int)rows, K, ldx,
+                                       static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, ldy, flags,
+                                       static_cast<cudaStream_t>(stream), site);
+}
+
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream) {
     if (!ws) {
         set_error("check_status: null workspace");

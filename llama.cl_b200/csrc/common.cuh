@@ -62,6 +62,15 @@ int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uin
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
                              cudaStream_t s);
+// the same kernel with outputs stored, epoch-stamped, into every rank's buffer (tp->y_peer)
+int launch_fc_decode_cluster_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
+                                int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,
+                                const q4fc_tp_site* tp);
+// step barrier and stream-side wait of the N-split over several GPUs
+int launch_tp_step_begin(unsigned long long* epoch, unsigned long long* const* barrier_peer,
+                         const unsigned long long* barrier_local, int world, int* status, cudaStream_t s);
+int launch_tp_collect(const unsigned long long* src, int64_t rows, int64_t N, int64_t ld, float* dst, int64_t ldd,
+                      const unsigned long long* epoch, int* status, cudaStream_t s);
 int choose_cluster_count(int64_t Ng, int64_t nc_cap);
 size_t prefill_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int G);
 int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,

@@ -1,494 +1,8 @@
-// Decode FC (rows <= 8), cluster form: the default kernel behind q4fc_fc_decode.
-// Same arithmetic as fc_decode.cu (reference: fc_Q4A, ops/op_fc.hpp:286-426);
-// what differs is how the work is cut and how partial sums meet.
-//
-// Decomposition.  A thread-block cluster of `cs` CTAs owns a contiguous range
-// of stripes (32 output columns each).  CTA rank j of the cluster owns the K
-// slice kb in [j*Kg/cs, (j+1)*Kg/cs) of every one of those stripes.  So
-//   * a CTA only ever needs the activations of its own K slice: it quantizes
-//     rows x K/cs values instead of rows x K (the quantization is spread over
-//     the cluster with no redundancy inside it);
-//   * partial sums of one stripe are pushed over distributed shared memory
-//     into the CTA that owns the stripe's output (rank = stripe mod cs) and
-//     added there in rank order after one cluster barrier -- no global
-//     scratch, no atomics, fixed summation order.
-// Inside a CTA the (stripes x K-slice) rectangle is flattened and split into
-// equal contiguous runs per warp; a run is a sequence of `Kc`-block pieces,
-// each piece contiguous in memory (Kc*BS bytes).
-//
-// Streaming.  As in fc_decode.cu a lane loads 128 bits of nibbles (4 columns
-// x 8 k) straight from global memory and feeds mma.sync.m16n8k32 (u8 x s8 ->
-// s32); two steps per warp are in flight in registers and both are issued
-// before the programmatic-dependent-launch wait, because weights never depend
-// on the preceding kernel.
-//
-// A run longer than the two register steps is also requested into L2 with
-// cp.async.bulk.prefetch before the wait, so HBM keeps streaming while the
-// preceding kernel drains.
-//
-// Activations.  A warp reads 128 consecutive k of a row of the CTA's slice
-// (one 128-bit load per lane, a few in flight) and quantizes them in
-// registers by the rules of FC_dynamic_quantize_x (ops/op_fc.hpp:246-268,
-// ops/utils.hpp:200-220): codes and scales bit-equal to the reference's, group
-// sums tree-ordered.
-#include <cooperative_groups.h>
-
-#include "common.cuh"
-
-namespace cg = cooperative_groups;
-
-// Phase timestamps for tuning builds (-DQ4FC_TIMELINE): lane 0 of every warp records %globaltimer
-// at phase boundaries into a buffer set with q4fc_debug_set_timeline().  Compiled out otherwise.
-#ifdef Q4FC_TIMELINE
-__device__ long long* g_timeline = nullptr;
-__device__ __forceinline__ long long gtime() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define Q4FC_MARK(k)                                                                       \
-    do {                                                                                   \
-        if (g_timeline && (threadIdx.x & 31) == 0)                                         \
-            g_timeline[((long long)blockIdx.x * kCW + (threadIdx.x >> 5)) * 16 + (k)] = gtime(); \
-    } while (0)
-extern "C" __attribute__((visibility("default"))) int q4fc_debug_set_timeline(long long* buf) {
-    return (int)cudaMemcpyToSymbol(g_timeline, &buf, sizeof(buf));
-}
-#else
-#define Q4FC_MARK(k) \
-    do {             \
-    } while (0)
-#endif
+// Single-GPU instantiations of the cluster decode kernel (fc_decode_cluster_impl.cuh, TP = false).
+#define Q4FC_TIMELINE_SETTER q4fc_debug_set_timeline
+#include "fc_decode_cluster_impl.cuh"
 
 namespace q4fc {
-namespace {
-
-constexpr int kCW = 4;  // warps per CTA
-constexpr int kCThreads = kCW * 32;
-constexpr int kMaxStripes = 16;  // stripes per cluster (bounds the shared-memory inbox)
-constexpr uint32_t kNibMask = 0x0F0F0F0Fu;
-
-struct ClusterParams {
-    const float* x;
-    float* y;
-    const uint8_t* wq;
-    int64_t K, ldx, N, ldy;
-    int rows, Ng, Kg;
-    int cs, log2cs, nc;  // CTAs per cluster (a power of two), clusters
-    int sq, sr;          // stripes per cluster: sq, the first sr clusters one more
-    int kq, kr;          // K groups per rank: kq, the first kr ranks one more
-    int slice_k;         // elements of the widest K slice: (kq + (kr > 0)) * G
-    int code_stride;     // bytes between code rows in shared memory
-    int pmax;            // most warps that can share one stripe's slice inside a CTA
-    int slot_f;          // floats per inbox slot: 32 columns x rows (rounded up to 2)
-    int inbox_slots;     // per-CTA inbox: owned stripes x cs x pmax slots
-    int x_vec_ok;
-};
-
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm(  // a pure function of its operands: left to the scheduler to interleave
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// request `bytes` (multiple of 16, 16-byte aligned) starting at p into L2; nothing waits for it
-__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-// cluster barrier, split so that the arrival can be posted early
-__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
-template <int G, int QTYPE>
-struct Cl {
-    static constexpr int BS = block_bytes(QTYPE, G);
-    static constexpr int SETS = G / 32;
-    static constexpr int NBLK = (G == 32) ? 4 : 1;
-    struct Step {
-        uint4 q[NBLK][SETS];
-        uint2 wd[NBLK];
-        uint2 wm[NBLK];
-    };
-};
-
-template <int G, int QTYPE, bool SIGNED, int ROWS>
-__global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const ClusterParams p) {
-    using C = Cl<G, QTYPE>;
-    constexpr int BS = C::BS;
-    constexpr int SETS = C::SETS;
-    constexpr int NBLK = C::NBLK;
-
-    extern __shared__ __align__(16) uint8_t smem[];
-    // [inbox: inbox_slots x slot_f f32][sc: kc_max x 16 f32][codes: rows x code_stride]
-    float* inbox = reinterpret_cast<float*>(smem);
-    float* sc = inbox + p.inbox_slots * p.slot_f;
-    const int kc_max = p.slice_k / G;
-    uint8_t* codes = reinterpret_cast<uint8_t*>(sc + kc_max * 16);
-
-    cg::cluster_group cluster = cg::this_cluster();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int cs = p.cs;
-    const int j = (int)(blockIdx.x & (cs - 1));  // rank in the cluster (clusters are consecutive CTAs)
-    const int c = (int)(blockIdx.x >> p.log2cs);
-    const int s0 = c * p.sq + min(c, p.sr);
-    const int r = p.sq + (c < p.sr ? 1 : 0);
-    const int k0 = j * p.kq + min(j, p.kr);
-    const int Kc = p.kq + (j < p.kr ? 1 : 0);  // >= 1: the launcher keeps cs <= Kg
-    const int F = r * Kc;
-    const int f0 = (warp * F) / kCW;
-    const int f1 = ((warp + 1) * F) / kCW;
-
-    Q4FC_MARK(0);
-    pdl_launch_dependents();
-
-    // the inbox starts at zero (slots nobody writes to add nothing); first phase of the cluster
-    // barrier: "my inbox is clean", posted before any load so that its release waits for nothing
-    for (int i = threadIdx.x; i < p.inbox_slots * (p.slot_f / 4); i += kCThreads)
-        reinterpret_cast<float4*>(inbox)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    Q4FC_MARK(8);
-    if (cs > 1) cluster_arrive_release();
-    Q4FC_MARK(9);
-
-    // ---- weights: two steps in flight in registers, the rest of the run requested into L2
-    typename C::Step cur, nxt;
-    int fl = f0;                     // next block to load
-    int li = f0 / Kc, lk = f0 - li * Kc;  // its (stripe, kb) inside the rectangle
-    const int ci0 = li, ck0 = lk;
-    const uint8_t* lane_base = p.wq + t * 128 + g * 16;
-    auto load_step = [&](typename C::Step& s) {
-#pragma unroll
-        for (int i = 0; i < NBLK; i++) {
-            if (fl < f1) {
-                const uint8_t* blk = lane_base + ((int64_t)(s0 + li) * p.Kg + k0 + lk) * BS;
-#pragma unroll
-                for (int jj = 0; jj < SETS; jj++) s.q[i][jj] = ldg_stream_v4(blk + jj * 512);
-                const uint8_t* tail = blk - t * 128 - g * 8 + 16 * G;  // wd of columns 4g..4g+3
-                s.wd[i] = ldg_stream_v2(tail);
-                if (QTYPE == 1) s.wm[i] = ldg_stream_v2(tail + 64);
-                fl++;
-                if (++lk == Kc) lk = 0, li++;
-            }
-        }
-    };
-    load_step(cur);
-    load_step(nxt);
-    Q4FC_MARK(10);
-    if (f1 - f0 > 2 * NBLK) {
-        const int pf = f0 + 2 * NBLK;
-        const int i_first = pf / Kc, i_last = (f1 - 1) / Kc;
-        for (int i = i_first + lane; i <= i_last; i += 32) {  // one contiguous piece per stripe
-            const int fb = max(pf, i * Kc), fe = min(f1, (i + 1) * Kc);
-            const uint8_t* a = p.wq + ((int64_t)(s0 + i) * p.Kg + k0 + (fb - i * Kc)) * BS;
-            for (int done = 0; done < fe - fb; done += 16)
-                l2_prefetch(a + (int64_t)done * BS, (uint32_t)(min(16, fe - fb - done) * BS));
-        }
-    }
-
-    Q4FC_MARK(1);
-    pdl_wait_prior_grid();
-    Q4FC_MARK(2);
-
-    // ---- quantize this CTA's K slice of the activation rows (ops/op_fc.hpp:246-268)
-    {
-        constexpr int SEG = G / 4;    // lanes per group
-        constexpr int GPC = 128 / G;  // groups per 128-k chunk
-        const int Ls = Kc * G;        // slice length per row
-        const int64_t kbase = (int64_t)k0 * G;
-        const int chunks = (Ls + 127) >> 7;
-        const int e0 = (lane % SEG) * 4;
-        for (int ch = warp; ch < chunks; ch += kCW) {
-            const int e = ch * 128 + lane * 4;  // element inside the slice
-            const int64_t k = kbase + e;
-            const int kbl = ch * GPC + lane / SEG;
-            const bool exists = kbl < Kc;
-            const int len = exists ? (int)min((int64_t)G, p.K - (kbase + (int64_t)kbl * G)) : 0;
-            const int body = len & ~7;
-            const bool vec = p.x_vec_ok && (e < Ls) && (k + 4 <= p.K);
-            float v[ROWS][4];
-#pragma unroll
-            for (int m = 0; m < ROWS; m++) {
-                v[m][0] = v[m][1] = v[m][2] = v[m][3] = 0.0f;
-                if (m < p.rows && e < Ls) {
-                    const float* src = p.x + m * p.ldx + k;
-                    if (vec) {
-                        const float4 a = __ldcg(reinterpret_cast<const float4*>(src));
-                        v[m][0] = a.x, v[m][1] = a.y, v[m][2] = a.z, v[m][3] = a.w;
-                    } else {
-#pragma unroll
-                        for (int jj = 0; jj < 4; jj++)
-                            if (k + jj < p.K) v[m][jj] = __ldcg(src + jj);
-                    }
-                }
-            }
-            // all ROWS rows go through the same straight-line code (rows beyond p.rows are zero),
-            // so the independent shuffle / divide chains of the rows overlap
-            float amax[ROWS], fsum[ROWS];
-#pragma unroll
-            for (int m = 0; m < ROWS; m++) {
-                amax[m] = 0.0f, fsum[m] = 0.0f;
-#pragma unroll
-                for (int jj = 0; jj < 4; jj++)
-                    if (e0 + jj < len) {
-                        amax[m] = fmaxf(amax[m], fabsf(v[m][jj]));
-                        fsum[m] += v[m][jj];
-                    }
-            }
-#pragma unroll
-            for (int off = SEG / 2; off > 0; off >>= 1) {
-#pragma unroll
-                for (int m = 0; m < ROWS; m++) {
-                    amax[m] = fmaxf(amax[m], __shfl_xor_sync(0xffffffffu, amax[m], off));
-                    fsum[m] += __shfl_xor_sync(0xffffffffu, fsum[m], off);
-                }
-            }
-#pragma unroll
-            for (int m = 0; m < ROWS; m++) {
-                const float d = div_const_rn(amax[m], 127.0f, 1.0f / 127.0f);
-                const float id = inv_or_zero(d);
-                uint32_t packed = 0;
-                int isum = 0;
-#pragma unroll
-                for (int jj = 0; jj < 4; jj++) {
-                    int q = 0;
-                    if (e0 + jj < len) {
-                        const float tq = __fmul_rn(v[m][jj], id);
-                        if (e0 + jj < body) {
-                            q = __float2int_rn(tq);  // 8-wide body of the reference: nearest even
-                        } else {
-                            const float h = __int_as_float((__float_as_int(tq) & 0x80000000) | 0x3F000000);
-                            q = __float2int_rz(__fadd_rz(tq, h));  // its scalar tail: half away
-                        }
-                        q = min(127, max(-128, q));
-                    }
-                    isum += q;
-                    packed |= (uint32_t)(q & 0xFF) << (8 * jj);
-                }
-                if (SIGNED) {
-#pragma unroll
-                    for (int off = SEG / 2; off > 0; off >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, off);
-                }
-                if (exists && m < p.rows) {
-                    *reinterpret_cast<uint32_t*>(codes + m * p.code_stride + e) = packed;
-                    if (e0 == 0) {
-                        // the reference's 1/16 activation scale and x16 nibble shift of Q4_0 cancel exactly
-                        sc[kbl * 16 + m * 2 + 0] = d;
-                        sc[kbl * 16 + m * 2 + 1] = SIGNED ? __int_as_float(8 * isum) : fsum[m];
-                    }
-                }
-            }
-        }
-    }
-    Q4FC_MARK(3);
-    __syncthreads();                     // codes and scales of the slice are ready (and this CTA's inbox is clean)
-    if (cs > 1) cluster_wait_acquire();  // every inbox of the cluster is clean: pushes are allowed
-    Q4FC_MARK(4);
-
-    // ---- stream this warp's run; every finished piece is pushed to the stripe's owner:
-    //      CTA (i mod cs), slot ((i / cs) * cs + sender rank) * warps + sender warp
-    float acc[4][2];
-#pragma unroll
-    for (int i = 0; i < 4; i++) acc[i][0] = acc[i][1] = 0.0f;
-    int f = f0;
-    int ci = ci0, ck = ck0;  // compute cursor
-    const uint8_t* my_codes = codes + g * p.code_stride + 8 * t;
-    const bool row_live = g < p.rows;
-
-    auto push = [&](int stripe_l) {
-        // piece number = this warp's position among the warps that share the stripe's slice
-        const int w_first = min(kCW - 1, (kCW * (stripe_l * Kc + 1) + F - 1) / F - 1);
-        const int slot = (((stripe_l >> p.log2cs) << p.log2cs) + j) * p.pmax + (warp - w_first);
-        float* dst = inbox + slot * p.slot_f;
-        const int owner = stripe_l & (cs - 1);
-        if (owner != j) dst = cluster.map_shared_rank(dst, owner);
-#pragma unroll
-        for (int mi = 0; mi < 2; mi++)
-            if ((2 * t + mi) * 32 < p.slot_f)
-                *reinterpret_cast<float4*>(dst + (2 * t + mi) * 32 + g * 4) =
-                    make_float4(acc[0][mi], acc[1][mi], acc[2][mi], acc[3][mi]);
-#pragma unroll
-        for (int i = 0; i < 4; i++) acc[i][0] = acc[i][1] = 0.0f;
-    };
-
-    auto process = [&](const typename C::Step& st) {
-#pragma unroll
-        for (int i = 0; i < NBLK; i++) {
-            if (f + i < f1) {
-                // two accumulator chains per tile (even / odd row sets) halve the dependent-MMA latency
-                int ia[4] = {0, 0, 0, 0}, ib[4] = {0, 0, 0, 0}, ja[4] = {0, 0, 0, 0}, jb[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int jj = 0; jj < SETS; jj++) {
-                    uint2 xb = make_uint2(0u, 0u);
-                    if (row_live) xb = *reinterpret_cast<const uint2*>(my_codes + ck * G + 32 * jj);
-                    const uint4 q = st.q[i][jj];
-                    uint32_t l0 = q.x & kNibMask, l1 = q.y & kNibMask, l2 = q.z & kNibMask, l3 = q.w & kNibMask;
-                    uint32_t h0 = (q.x >> 4) & kNibMask, h1 = (q.y >> 4) & kNibMask, h2 = (q.z >> 4) & kNibMask,
-                             h3 = (q.w >> 4) & kNibMask;
-                    if (SIGNED) {
-                        l0 ^= 0x08080808u, l1 ^= 0x08080808u, l2 ^= 0x08080808u, l3 ^= 0x08080808u;
-                        h0 ^= 0x08080808u, h1 ^= 0x08080808u, h2 ^= 0x08080808u, h3 ^= 0x08080808u;
-                    }
-                    if (jj & 1) {
-                        mma_u8s8(ja, l0, l1, h0, h1, xb.x, xb.y);
-                        mma_u8s8(jb, l2, l3, h2, h3, xb.x, xb.y);
-                    } else {
-                        mma_u8s8(ia, l0, l1, h0, h1, xb.x, xb.y);
-                        mma_u8s8(ib, l2, l3, h2, h3, xb.x, xb.y);
-                    }
-                }
-#pragma unroll
-                for (int q = 0; q < 4; q++) ia[q] += ja[q], ib[q] += jb[q];
-                const float4 s4 = *reinterpret_cast<const float4*>(sc + ck * 16 + t * 4);  // xs0, gs0, xs1, gs1
-                const float2 wd01 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].x));
-                const float2 wd23 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].y));
-                const float wdf[4] = {wd01.x, wd01.y, wd23.x, wd23.y};
-                const int iv[4][2] = {{ia[0], ia[1]}, {ia[2], ia[3]}, {ib[0], ib[1]}, {ib[2], ib[3]}};
-                const float xs[2] = {s4.x, s4.z};
-                const float gs[2] = {s4.y, s4.w};
-                float wmf[4] = {0.f, 0.f, 0.f, 0.f};
-                if (QTYPE == 1) {
-                    const float2 wm01 = __half22float2(*reinterpret_cast<const __half2*>(&st.wm[i].x));
-                    const float2 wm23 = __half22float2(*reinterpret_cast<const __half2*>(&st.wm[i].y));
-                    wmf[0] = wm01.x, wmf[1] = wm01.y, wmf[2] = wm23.x, wmf[3] = wm23.y;
-                }
-#pragma unroll
-                for (int cc = 0; cc < 4; cc++) {
-#pragma unroll
-                    for (int mi = 0; mi < 2; mi++) {
-                        int I = iv[cc][mi];
-                        if (SIGNED) I -= __float_as_int(gs[mi]);
-                        acc[cc][mi] = fmaf(__fmul_rn(wdf[cc], xs[mi]), (float)I, acc[cc][mi]);
-                        if (QTYPE == 1) acc[cc][mi] = fmaf(wmf[cc], gs[mi], acc[cc][mi]);
-                    }
-                }
-                if (++ck == Kc) {  // end of this stripe's slice
-                    push(ci);
-                    ck = 0, ci++;
-                }
-            }
-        }
-    };
-
-    while (true) {
-        if (f >= f1) break;
-        process(cur);
-        f += NBLK;
-        load_step(cur);
-        if (f >= f1) break;
-        process(nxt);
-        f += NBLK;
-        load_step(nxt);
-    }
-    if (ck != 0 && f1 > f0) push(ci);  // the run ended inside a stripe's slice
-    Q4FC_MARK(5);
-
-    // ---- every piece has been pushed: the owner adds its stripes in (rank, warp) order
-    if (cs > 1) {
-        cluster_arrive_release();
-        cluster_wait_acquire();
-    } else {
-        __syncthreads();
-    }
-    Q4FC_MARK(6);
-    for (int i = j + cs * warp; i < r; i += cs * kCW) {
-        const float* src = inbox + ((i >> p.log2cs) << p.log2cs) * p.pmax * p.slot_f;
-        const int64_t n = (int64_t)(s0 + i) * 32 + lane;
-        const int nsl = cs * p.pmax;
-#pragma unroll
-        for (int m = 0; m < ROWS; m++) {
-            if (m < p.rows) {
-                float sum = 0.0f;
-                for (int q = 0; q < nsl; q++) sum += src[q * p.slot_f + m * 32 + lane];
-                if (n < p.N) p.y[m * p.ldy + n] = sum;
-            }
-        }
-    }
-    Q4FC_MARK(7);
-    // no CTA touches another CTA's shared memory after the barrier above, so exiting is safe
-}
-
-// one launchable instantiation: its function pointer plus lazily set attributes
-struct Variant {
-    const void* fn;
-    bool attr_done[64];
-    int max_clusters[64][4];  // [device][log2 cs], 0 = not queried yet
-};
-
-template <int G, int QTYPE, bool SIGNED, int ROWS>
-Variant* variant_of() {
-    static Variant v = {reinterpret_cast<const void*>(&fc_decode_cluster_kernel<G, QTYPE, SIGNED, ROWS>), {}, {}};
-    return &v;
-}
-
-template <int G, int QTYPE, bool SIGNED>
-Variant* variant_for_rows(int rows) {
-    if (rows <= 1) return variant_of<G, QTYPE, SIGNED, 1>();
-    if (rows <= 2) return variant_of<G, QTYPE, SIGNED, 2>();
-    if (rows <= 4) return variant_of<G, QTYPE, SIGNED, 4>();
-    return variant_of<G, QTYPE, SIGNED, 8>();
-}
-
-Variant* pick_variant(int qtype, int G, bool sgn, int rows) {
-    if (qtype == 1 && G == 32) return variant_for_rows<32, 1, false>(rows);
-    if (qtype == 1 && G == 128) return variant_for_rows<128, 1, false>(rows);
-    if (qtype == 0 && G == 32 && !sgn) return variant_for_rows<32, 0, false>(rows);
-    if (qtype == 0 && G == 128 && !sgn) return variant_for_rows<128, 0, false>(rows);
-    if (qtype == 0 && G == 32) return variant_for_rows<32, 0, true>(rows);
-    return variant_for_rows<128, 0, true>(rows);
-}
-
-void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, int cs, size_t smem, bool pdl,
-                        cudaStream_t s) {
-    cfg = cudaLaunchConfig_t{};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kCThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    int nattr = 0;
-    attr[nattr].id = cudaLaunchAttributeClusterDimension;
-    attr[nattr].val.clusterDim.x = (unsigned)cs;
-    attr[nattr].val.clusterDim.y = 1;
-    attr[nattr].val.clusterDim.z = 1;
-    nattr++;
-    if (pdl) {
-        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
-        nattr++;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = nattr;
-}
-
-// clusters of `cs` CTAs that can be resident at once (hardware placement included), cached
-int max_resident_clusters(Variant* v, int dev, int cs, int log2cs, const DeviceInfo* di) {
-    if (dev >= 64) return di->sm_count * 4 / cs;
-    if (!v->attr_done[dev]) {
-        if (cudaFuncSetAttribute(v->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin) !=
-            cudaSuccess) {
-            cudaGetLastError();
-            return -1;
-        }
-        v->attr_done[dev] = true;
-    }
-    if (v->max_clusters[dev][log2cs] == 0) {
-        cudaLaunchConfig_t cfg;
-        cudaLaunchAttribute attr[2];
-        fill_launch_config(cfg, attr, cs, cs, 56 * 1024, false, nullptr);  // shared memory never exceeds this per CTA
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, v->fn, &cfg) != cudaSuccess || n <= 0) {
-            cudaGetLastError();
-            n = di->sm_count * 2 / cs;  // conservative stand-in
-            if (n < 1) n = 1;
-        }
-        v->max_clusters[dev][log2cs] = n;
-    }
-    return v->max_clusters[dev][log2cs];
-}
-
-}  // namespace
 
 // Picks the number of clusters for a shape.  Every cluster quantizes the whole
 // activation once (spread over its CTAs), so few large clusters are preferred.
@@ -514,55 +28,7 @@ int choose_cluster_count(int64_t Ng, int64_t nc_cap) {
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
                              cudaStream_t s) {
-    if (rows == 0 || N == 0) return Q4FC_OK;
-    const DeviceInfo* di = device_info();
-    if (!di) return Q4FC_ECUDA;
-    if (Ng * Kg >= 0x7fffffffLL) {
-        set_error("fc_decode: %lld blocks exceed the 2^31 limit", (long long)(Ng * Kg));
-        return Q4FC_ELIMIT;
-    }
-    ClusterParams p;
-    p.x = x, p.y = y, p.wq = wq;
-    p.K = K, p.ldx = ldx, p.N = N, p.ldy = ldy;
-    p.rows = rows, p.Ng = (int)Ng, p.Kg = (int)Kg;
-    const bool sgn = (flags & Q4FC_FLAG_NIBBLE_SIGNED) && qtype == 0;
-    const bool pdl = (flags & Q4FC_FLAG_PDL) != 0;
-    Variant* v = pick_variant(qtype, G, sgn, rows);
-    int dev = 0;
-    Q4FC_CUDA_OK(cudaGetDevice(&dev));
-    p.cs = 8;
-    while (p.cs > 1 && p.cs > Kg) p.cs /= 2;
-    p.log2cs = 0;
-    while ((1 << p.log2cs) < p.cs) p.log2cs++;
-    int cap = max_resident_clusters(v, dev, p.cs, p.log2cs, di);
-    if (cap < 0) return cuda_fail(cudaErrorUnknown, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
-    // in a chain launched with programmatic serialization two kernels share the GPU: the next one
-    // streams its weights toward L2 while this one finishes, so each takes half of the CTA slots
-    if (pdl && cap >= 2) cap /= 2;
-    p.nc = choose_cluster_count(Ng, cap);
-    p.sq = (int)(Ng / p.nc), p.sr = (int)(Ng % p.nc);
-    p.kq = (int)(Kg / p.cs), p.kr = (int)(Kg % p.cs);
-    const int kc_max = p.kq + (p.kr > 0 ? 1 : 0);
-    p.slice_k = kc_max * G;
-    p.code_stride = (p.slice_k + 127) / 128 * 128 + 32;  // rows 32 B apart modulo 128: conflict-free 8-byte operand loads
-    const int r_max = p.sq + (p.sr > 0 ? 1 : 0);
-    p.pmax = (kCW + p.sq - 1) / p.sq + 1;  // a slice of Kc blocks meets at most ceil(kCW / r) + 1 warp runs
-    if (p.pmax > kCW) p.pmax = kCW;
-    p.slot_f = 32 * ((rows + 1) / 2 * 2);
-    p.inbox_slots = (r_max + p.cs - 1) / p.cs * p.cs * p.pmax;  // owned stripes x senders x pieces
-    p.x_vec_ok = (K % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
-    const size_t smem = (size_t)p.inbox_slots * p.slot_f * 4 + (size_t)kc_max * 64 + (size_t)rows * p.code_stride;
-    if (smem > (size_t)di->max_smem_optin) {
-        set_error("fc_decode: rows=%d K=%lld needs %zu bytes of shared memory (limit %d)", rows, (long long)K, smem,
-                  di->max_smem_optin);
-        return Q4FC_ELIMIT;
-    }
-    cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[2];
-    fill_launch_config(cfg, attr, p.nc * p.cs, p.cs, smem, pdl, s);
-    void* args[] = {const_cast<ClusterParams*>(&p)};
-    Q4FC_CUDA_OK(cudaLaunchKernelExC(&cfg, v->fn, args));
-    return Q4FC_OK;
+    return launch_cluster_impl<false>(x, rows, K, ldx, wq, Ng, Kg, qtype, G, N, y, ldy, flags, s, nullptr);
 }
 
 }  // namespace q4fc

@@ -120,3 +120,221 @@ class TPLinearQ4:
         # valid columns of the concatenation are exactly [0, N)
         y = gathered.permute(1, 0, 2).reshape(rows, self.world * self.cols)
         return y[:, : self.N].reshape(B, M, self.N).contiguous()
+
+
+# --------------------------------------------------------------------------
+# Fused form: the FC kernel itself delivers its columns to every rank.
+# --------------------------------------------------------------------------
+class _DeviceView:
+    """Minimal ``__cuda_array_interface__`` carrier so that torch can view arena memory as a tensor."""
+
+    def __init__(self, ptr: int, shape: tuple[int, ...], typestr: str) -> None:
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class TPArena:
+    """Peer-mapped device memory with the same layout on every rank of ``group``.
+
+    Each rank allocates ``nbytes`` through the C-ABI (``q4fc_tp_arena_create``), the 64-byte IPC handles
+    travel by ``all_gather_object`` and every rank maps all the others (``q4fc_tp_arena_open``).  ``alloc``
+    is a bump allocator: ranks must make the same calls in the same order, which gives symmetric offsets.
+    The first 256 bytes hold the status word."""
+
+    STATUS, HEADER = 8, 256
+
+    def __init__(self, nbytes: int, device: torch.device, group=None) -> None:
+        import ctypes as C
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if not 1 <= self.world <= 8:
+            raise RuntimeError(f"TPArena: world size {self.world} outside 1..8")
+        self.device = torch.device(device)
+        self.nbytes = int(nbytes)
+        self._top = self.HEADER
+        L = _cabi.lib()
+        base = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _cabi.check(L.q4fc_tp_arena_create(self.nbytes, C.byref(base), handle), "tp_arena_create")
+        self.local = int(base.value)
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.bases: list[int] = []
+        self._opened: list[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.bases.append(self.local)
+                continue
+            peer = C.c_void_p()
+            with torch.cuda.device(self.device):
+                _cabi.check(L.q4fc_tp_arena_open(h, C.byref(peer)), f"tp_arena_open(rank {r})")
+            self.bases.append(int(peer.value))
+            self._opened.append(int(peer.value))
+        dist.barrier(group=group)  # every rank has mapped every arena before anyone stores into one
+
+    # ---- layout
+    def alloc(self, nbytes: int, align: int = 256) -> int:
+        off = (self._top + align - 1) // align * align
+        if off + nbytes > self.nbytes:
+            raise RuntimeError(f"TPArena: {nbytes} bytes requested, {self.nbytes - off} left of {self.nbytes}")
+        self._top = off + int(nbytes)
+        return off
+
+    def peers(self, off: int) -> list[int]:
+        return [b + off for b in self.bases]
+
+    def tensor(self, off: int, shape: tuple[int, ...], dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """This rank's arena memory at ``off`` as a tensor (no copy)."""
+        typestr = {torch.float32: "<f4", torch.int32: "<i4", torch.int64: "<i8", torch.uint8: "|u1"}[dtype]
+        return torch.as_tensor(_DeviceView(self.local + off, tuple(shape), typestr), device=self.device)
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def status(self) -> int:
+        """The status word (synchronizes the device): non-zero after a bounded wait ran out."""
+        torch.cuda.synchronize(self.device)
+        return int(self.tensor(self.STATUS, (1,), torch.int32).item())
+
+    def check(self) -> None:
+        st = self.status()
+        if st != 0:
+            raise RuntimeError(f"TP status word = {st:#x}: a bounded wait on the other ranks ran out")
+
+    def close(self) -> None:
+        """Collective: unmap the peers' arenas, then free this one after everybody has unmapped it."""
+        L = _cabi.lib()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for p in self._opened:
+            L.q4fc_tp_arena_close(p)
+        self._opened = []
+        dist.barrier(group=self.group)
+        if self.local:
+            L.q4fc_tp_arena_destroy(self.local)
+            self.local = 0
+
+
+class TPSchedule:
+    """A fixed set of fused FCs that always run together, once each per step, with its own step counter.
+
+    Outputs are stamped with the schedule's epoch and readers wait for the current stamp, so every FC of
+    the schedule must run in every step of the schedule and in no other.  Independent pieces of work
+    (another model, a stand-alone FC) get their own schedule."""
+
+    def __init__(self, arena: TPArena) -> None:
+        import ctypes as C
+
+        self.arena = arena
+        off = arena.alloc(256, 256)
+        self.epoch_off, self.barrier_off = off, off + 128
+        self._barrier_peers = (C.c_void_p * 8)(*arena.peers(self.barrier_off))
+
+    def step_begin(self) -> None:
+        """Advance the epoch and meet the other ranks (one tiny kernel on the current stream)."""
+        a = self.arena
+        _cabi.check(_cabi.lib().q4fc_tp_step_begin(a.local + self.epoch_off, self._barrier_peers,
+                                                   a.local + self.barrier_off, a.world, a.local + a.STATUS,
+                                                   a._stream()), "tp_step_begin")
+
+
+class StampedOutput:
+    """What a fused FC returns: this rank's buffer of (value, epoch) words, ``[rows, ld]``, filled by all
+    ranks' kernels.  Feed it to the next fused FC as it is (that kernel waits word by word), or call
+    ``tensor()`` for plain fp32."""
+
+    def __init__(self, layer: "FusedTPLinearQ4", B: int, M: int) -> None:
+        self.layer, self.B, self.M = layer, B, M
+        self.rows, self.N, self.ld = B * M, layer.N, layer.ldy
+        self.ptr = layer.arena.local + layer.y_off
+
+    @property
+    def shape(self) -> tuple[int, int, int]:
+        return (self.B, self.M, self.N)
+
+    def tensor(self, out: torch.Tensor | None = None) -> torch.Tensor:
+        """fp32 ``[B, M, N]`` on the current stream: one small kernel that waits for every word of this
+        step and unpacks it.  ``out`` (contiguous) is reused when given."""
+        lay, a = self.layer, self.layer.arena
+        if out is None:
+            out = torch.empty((self.B, self.M, self.N), dtype=torch.float32, device=a.device)
+        elif out.shape != self.shape or out.dtype != torch.float32 or not out.is_contiguous():
+            raise RuntimeError("StampedOutput.tensor: out must be a contiguous fp32 [B, M, N] tensor")
+        _cabi.check(_cabi.lib().q4fc_tp_collect(self.ptr, self.rows, self.N, self.ld, out.data_ptr(), self.N,
+                                                a.local + lay.schedule.epoch_off, a.local + a.STATUS,
+                                                a._stream()), "tp_collect")
+        return out
+
+
+class FusedTPLinearQ4:
+    """N-split FC whose kernel stores its columns into every rank's output buffer (``q4fc_fc_decode_tp``).
+
+    A layer belongs to a ``TPSchedule`` and runs exactly once in each of its steps, after ``step_begin()``.
+    ``y = layer(x)``: ``x`` is a replicated fp32 ``[B, M, K]`` tensor, or the ``StampedOutput`` of another
+    layer of the same schedule -- then this layer's kernel waits for the other ranks' columns itself, word
+    by word, and nothing else is launched between the two FCs.  Rows per call are limited to 8 (the decode
+    kernel)."""
+
+    def __init__(self, schedule: TPSchedule, wq_shard: torch.Tensor, N: int, *, max_rows: int = 8,
+                 pdl: bool = False, nibble_signed: bool = False) -> None:
+        arena = schedule.arena
+        self.schedule = schedule
+        self.arena = arena
+        self.world, self.rank = arena.world, arena.rank
+        self.N = int(N)
+        self.Ng = (self.N + 31) // 32
+        self.nb0, self.nb1 = shard_bounds(self.Ng, self.world, self.rank)
+        self.n0, self.n1 = shard_rows(self.N, self.world, self.rank)
+        if wq_shard.shape[0] != self.nb1 - self.nb0:
+            raise RuntimeError(f"rank {self.rank}: shard has {wq_shard.shape[0]} stripes, expected {self.nb1 - self.nb0}")
+        self.weight = wq_shard
+        self.Kg = int(wq_shard.shape[1])
+        self.qtype, self.group_k = _cabi.infer_variant(wq_shard.shape[2])
+        self.max_rows = int(max_rows)
+        self.ldy = self.Ng * 32
+        self.y_off = arena.alloc(self.max_rows * self.ldy * 8)
+        self.flags = (_cabi.FLAG_PDL if pdl else 0) | (_cabi.FLAG_NIBBLE_SIGNED if nibble_signed else 0)
+        self._sites: dict = {}
+
+    def _site(self, stamped: bool) -> "_cabi.TpSite":
+        if stamped not in self._sites:
+            a = self.arena
+            s = _cabi.TpSite()
+            s.world = self.world
+            s.x_stamped = 1 if stamped else 0
+            s.col_off = self.nb0 * 32
+            for r in range(self.world):
+                s.y_peer[r] = a.bases[r] + self.y_off
+            s.epoch = a.local + self.schedule.epoch_off
+            s.status = a.local + a.STATUS
+            self._sites[stamped] = s
+        return self._sites[stamped]
+
+    def __call__(self, x: "torch.Tensor | StampedOutput") -> StampedOutput:
+        import ctypes as C
+
+        stamped = isinstance(x, StampedOutput)
+        if stamped:
+            if x.layer.schedule is not self.schedule:
+                raise RuntimeError("FusedTPLinearQ4: the input was produced under another schedule")
+            B, M, K = x.shape
+            rows, ldx, xptr = x.rows, x.ld, x.ptr
+        else:
+            B, M, K = x.shape
+            rows = B * M
+            if x.dtype != torch.float32 or x.stride(-1) != 1:
+                raise RuntimeError("FusedTPLinearQ4: x must be fp32 with unit stride along K")
+            x2 = x.reshape(rows, K)
+            ldx, xptr = (x2.stride(0) if rows > 1 else K), x2.data_ptr()
+        if rows > self.max_rows:
+            raise RuntimeError(f"FusedTPLinearQ4: {rows} rows exceed max_rows={self.max_rows}")
+        if (K + self.group_k - 1) // self.group_k != self.Kg:
+            raise RuntimeError(f"FusedTPLinearQ4: K={K} does not match the packed tensor's {self.Kg} groups")
+        _cabi.check(_cabi.lib().q4fc_fc_decode_tp(
+            xptr, rows, K, ldx, self.weight.data_ptr(), self.nb1 - self.nb0, self.Kg, self.qtype, self.group_k,
+            self.n1 - self.n0, self.ldy, C.byref(self._site(stamped)), self.flags, self.arena._stream()),
+            "fc_decode_tp")
+        return StampedOutput(self, B, M)

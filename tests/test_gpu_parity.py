@@ -406,3 +406,31 @@ def test_full_layer_pack_matches_oracle(pkg, oracle):
         for G in (32, 128):
             got = pkg.llmops.offline_FC_quant_Q4A(Wd, group_k=G).cpu().numpy()
             assert sha(got) == sha(oracle.restated.pack(W.numpy(), 1, G))
+
+
+def test_host_fc_graph_and_streams(lib_built):
+    """HostFC: host buffers in and out; the captured-graph form and the eager form give the same bytes as
+    the device-side call, for every row count, across repeated calls with fresh inputs."""
+    import llama_cl_b200 as pkg
+    from llama_cl_b200.host import HostFC
+
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(5)
+    N, K = 1000, 1024
+    W = (torch.randn(N, K, generator=g) * 0.02).to(dev)
+    wq = pkg.llmops.offline_FC_quant_Q4A(W, qtype="q4_1", group_k=128)
+    hg = HostFC(wq, N, max_rows=8, path="decode")
+    he = HostFC(wq, N, max_rows=8, graph=False, path="decode", stream=torch.cuda.Stream(dev))
+    for it in range(3):
+        for M in (1, 3, 8):
+            x = torch.randn(1, M, K, generator=g)
+            want = pkg.llmops.fc_Q4A(x.to(dev), wq, N, path="decode").cpu()
+            assert torch.equal(hg(x).clone(), want)
+            assert torch.equal(he(x.pin_memory()).clone(), want)
+            stage = hg.x_staging(M)
+            stage.copy_(x * 2)
+            y = hg(stage, sync=False)
+            hg.stream.synchronize()
+            assert torch.equal(y, pkg.llmops.fc_Q4A((x * 2).to(dev), wq, N, path="decode").cpu())
+    with pytest.raises(RuntimeError):
+        hg(torch.zeros(1, 9, K))

@@ -58,3 +58,133 @@ def test_tp_two_gpus_nccl(lib_built):
             p.join(300)
             assert p.exitcode == 0
     assert sorted(q.get(timeout=5) for _ in range(world)) == [(0, True), (1, True)]
+
+
+def _fused_worker(rank, world, initfile, result_q):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"file://{initfile}", rank=rank, world_size=world, device_id=dev)
+    notes = []
+    try:
+        import llama_cl_b200 as pkg
+        from llama_cl_b200 import tp
+
+        def expect(cond, what):
+            if not bool(cond):
+                notes.append(what)
+
+        arena = tp.TPArena(32 << 20, dev)
+        sched = tp.TPSchedule(arena)
+        H, I, NR = 4096, 11008, 4100  # NR: ragged tail (129 stripes: 65 + 64, last one 4 columns wide)
+        specs = {"q": (H, H, "q4_1", 128), "k": (H, H, "q4_1", 128), "up": (I, H, "q4_1", 128),
+                 "down": (H, I, "q4_1", 32), "last": (NR, H, "q4_0", 32)}
+        full, lay = {}, {}
+        for i, (name, (N, K, qname, G)) in enumerate(specs.items()):
+            g = torch.Generator().manual_seed(100 + i)
+            W = (torch.randn(N, K, generator=g) * 0.02).to(dev)
+            full[name] = pkg.llmops.offline_FC_quant_Q4A(W, qtype=qname, group_k=G)
+            n0, n1 = tp.shard_rows(N, world, rank)
+            shard = pkg.llmops.offline_FC_quant_Q4A(W[n0:n1].contiguous(), qtype=qname, group_k=G)
+            expect(torch.equal(shard, tp.shard_packed(full[name], world, rank)), f"{name}: shard bytes")
+            lay[name] = tp.FusedTPLinearQ4(sched, shard, N, pdl=True)
+
+        def chain(x):
+            """q, k side by side -> up(q) -> down -> last; every consumer waits inside its own kernel,
+            the unpacking kernels at the end wait for whatever is still in flight."""
+            sched.step_begin()
+            q = lay["q"](x)
+            k = lay["k"](x)
+            up = lay["up"](q)
+            down = lay["down"](up)
+            last = lay["last"](down)
+            return {n: o.tensor() for n, o in (("q", q), ("k", k), ("up", up), ("down", down), ("last", last))}
+
+        def verify(x, outs, tag):
+            got = {n: o.clone() for n, o in outs.items()}
+            ins = {"q": x, "k": x, "up": got["q"], "down": got["up"], "last": got["down"]}
+            for name, (N, K, _, _) in specs.items():
+                want = pkg.llmops.fc_Q4A(ins[name].contiguous(), full[name], N)
+                expect(got[name].shape == want.shape, f"{tag} {name}: shape {tuple(got[name].shape)}")
+                expect(torch.allclose(got[name], want, rtol=1e-3, atol=1e-4), f"{tag} {name}: differs from one GPU")
+                # a column is computed by exactly one rank and stored everywhere: ranks agree bit for bit
+                other = [torch.empty_like(got[name]) for _ in range(world)]
+                dist.all_gather(other, got[name].contiguous())
+                expect(all(torch.equal(o, got[name]) for o in other), f"{tag} {name}: ranks differ")
+
+        for rows in (1, 4):
+            for step in range(3):  # fresh input every step: stale data from the step before would show
+                g = torch.Generator().manual_seed(7 * rows + step)
+                x = torch.randn(1, rows, H, generator=g).to(dev)
+                outs = chain(x)
+                torch.cuda.synchronize()
+                verify(x, outs, f"rows={rows} step={step}")
+
+        # the same chain replayed as a CUDA graph: the epoch lives on the device, so replays advance it
+        xg = torch.zeros(1, 1, H, device=dev)
+        side = torch.cuda.Stream(dev)
+        with torch.cuda.stream(side):
+            chain(xg)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                outs_g = chain(xg)
+        torch.cuda.synchronize()
+        for step in range(3):
+            g = torch.Generator().manual_seed(900 + step)
+            xg.copy_(torch.randn(1, 1, H, generator=g))
+            graph.replay()
+            torch.cuda.synchronize()
+            verify(xg, outs_g, f"graph step={step}")
+        expect(arena.status() == 0, f"status {arena.status():#x} after the chains")
+
+        # a wait that nothing satisfies gives up after its limit, flags it, and leaves the context usable
+        ghost = tp.FusedTPLinearQ4(sched, tp.shard_packed(full["q"], world, rank), H)  # never run
+        tp.StampedOutput(ghost, 1, 1).tensor()
+        expect(arena.status() == 0x54505754, "the unsatisfied wait did not set the status word")
+        arena.tensor(arena.STATUS, (1,), torch.int32).zero_()
+        outs = chain(xg)
+        torch.cuda.synchronize()
+        verify(xg, outs, "after the timed-out wait")
+        expect(arena.status() == 0, "status after recovery")
+
+        # a second schedule in the same arena keeps its own step count: a stand-alone FC run twice
+        solo = tp.TPSchedule(arena)
+        one = tp.FusedTPLinearQ4(solo, tp.shard_packed(full["q"], world, rank), H)
+        for step in range(2):
+            solo.step_begin()
+            y = one(xg).tensor()
+            torch.cuda.synchronize()
+            want = pkg.llmops.fc_Q4A(xg, full["q"], H)
+            expect(torch.allclose(y, want, rtol=1e-3, atol=1e-4), f"solo schedule step {step}")
+        outs = chain(xg)  # and the first schedule is undisturbed by it
+        torch.cuda.synchronize()
+        verify(xg, outs, "after the solo schedule")
+        expect(arena.status() == 0, "status at the end")
+        arena.close()
+        result_q.put((rank, notes))
+    except Exception as e:  # report instead of leaving the parent to time out
+        import traceback
+
+        result_q.put((rank, notes + [traceback.format_exc()]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_two_gpus_fused_peer_stores(lib_built):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        procs = [ctx.Process(target=_fused_worker, args=(r, world, os.path.join(d, "init"), q)) for r in range(world)]
+        for p in procs:
+            p.start()
+        results = sorted(q.get(timeout=280) for _ in range(world))
+        for p in procs:
+            p.join(60)
+            if p.exitcode is None:
+                p.kill()  # exactly the processes started above
+    assert results == [(0, []), (1, [])], results
