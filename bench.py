@@ -282,6 +282,8 @@ def our_arm(args) -> None:
     # other order, timed as well: the per-launch roofline figure comes from that pass.
     n_lanes = 1 if tp_mode == "nccl" else max(1, args.lanes)  # one communicator: its collectives stay in order
     lane_streams = [torch.cuda.Stream(dev) for _ in range(n_lanes)]
+    # calls that may overlap on the GPU need separate workspaces
+    lane_ws = [pkg.llmops.Workspace(ws.nbytes, dev) for _ in range(n_lanes)]
 
     def deal(n: int):
         load, plan = [0.0] * n, [[] for _ in range(n)]
@@ -291,15 +293,16 @@ def our_arm(args) -> None:
             load[i] += packed_bytes(c["K"], c["n_local"]) / 5e12 + 4e-6 * (1 + c["M"] / 8)
         return plan
 
-    def run_calls(cs, pdl: bool = True) -> None:
+    def run_calls(cs, pdl: bool = True, wsp=None) -> None:
         outs = []
+        wsp = ws if wsp is None else wsp
         for c in cs:
             if fused:
                 outs.append((c, c["layer"](c["x"])))
             elif distributed:
                 c["layer"](c["x"])
             else:
-                pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=ws, pdl=pdl, path="decode")
+                pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=wsp, pdl=pdl, path="decode")
         # fused: unpack to plain fp32 behind the lane's FCs (each unpacking kernel waits for the other ranks'
         # columns), so that the step ends when every rank holds every full output
         for c, o in outs:
@@ -315,10 +318,10 @@ def our_arm(args) -> None:
             return
         start = torch.cuda.Event()
         start.record(cur)
-        for st, cs in zip(lane_streams, deal(lanes)):
+        for st, cs, wsp in zip(lane_streams, deal(lanes), lane_ws):
             st.wait_event(start)
             with torch.cuda.stream(st):
-                run_calls(cs)
+                run_calls(cs, wsp=wsp)
         for st in lane_streams[:lanes]:
             cur.wait_stream(st)
 
@@ -405,34 +408,31 @@ def our_arm(args) -> None:
         hosts = []
         for c in calls:
             if fused:
-                hosts.append(make_layer(tp.TPSchedule(arena), c["wq"], c["N"]))  # each call stands alone
+                hosts.append(tp.HostFusedFC(arena, c["wq"], c["N"], max_rows=8, pdl=True,
+                                            stream=lane_streams[len(hosts) % n_lanes]))
             elif distributed:
                 hosts.append(None)
             else:
-                hosts.append(HostFC(c["wq"], c["N"], max_rows=8, workspace=ws, path="decode",
-                                    stream=lane_streams[len(hosts) % n_lanes]))
-        # single GPU: the activations sit in the pinned input buffer of the call's HostFC
-        xs_host = [c["x"].cpu().pin_memory() if distributed else h.x_staging(c["M"]).copy_(c["x"].cpu())
+                hosts.append(HostFC(c["wq"], c["N"], max_rows=8, workspace=lane_ws[len(hosts) % n_lanes],
+                                    path="decode", stream=lane_streams[len(hosts) % n_lanes]))
+        # the activations sit in the pinned input buffer of the call's host front end
+        xs_host = [c["x"].cpu().pin_memory() if h is None else h.x_staging(c["M"]).copy_(c["x"].cpu())
                    for c, h in zip(calls, hosts)]
         ys_host = [torch.empty((1, c["M"], c["N"]), dtype=torch.float32).pin_memory() for c in calls]
 
         def step_e2e() -> None:
             for c, h, xh, yh in zip(calls, hosts, xs_host, ys_host):
                 if fused:
-                    c["x"].copy_(xh, non_blocking=True)
-                    h.schedule.step_begin()
-                    yh.copy_(h(c["x"]).tensor(out=c["y_full"]), non_blocking=True)
+                    h(xh, sync=False)
                 elif distributed:
                     c["x"].copy_(xh, non_blocking=True)
                     y = c["layer"](c["x"])
                     yh.copy_(y, non_blocking=True)
                 else:
                     h(xh, sync=False)
-            if distributed:
-                torch.cuda.current_stream(dev).synchronize()
-            else:
-                for st in lane_streams:
-                    st.synchronize()
+            torch.cuda.current_stream(dev).synchronize()
+            for st in lane_streams:
+                st.synchronize()
 
         n_e2e = max(3, min(args.steps, 200))
         for _ in range(3):
@@ -477,7 +477,16 @@ def our_arm(args) -> None:
                 return make_layer(None, wq_, N), wq_.numel()
             out = torch.empty((1, 1, N), device=dev, dtype=torch.float32)
             return (lambda x_, wq_=wq_, N=N, out=out: pkg.llmops.fc_Q4A(
-                x_, wq_, N, out=out, workspace=ws, pdl=True, path="decode")), wq_.numel()
+                x_, wq_, N, out=out, workspace=stream_ws(), pdl=True, path="decode")), wq_.numel()
+
+        ws_of_stream: dict = {}
+
+        def stream_ws():
+            """One workspace per stream: FCs running side by side must not share scratch."""
+            key = torch.cuda.current_stream(dev).cuda_stream
+            if key not in ws_of_stream:
+                ws_of_stream[key] = pkg.llmops.Workspace(ws.nbytes, dev)
+            return ws_of_stream[key]
 
         tok_sched = tp.TPSchedule(arena) if fused else None
         layers, stack_bytes_rank = [], 0

@@ -112,7 +112,11 @@ int q4fc_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int group
  * aligned, zeroed once with q4fc_fc_workspace_init() before its first use;
  * the kernels leave it ready for the next call.  Calls that may overlap on
  * the GPU need separate workspaces.  q4fc_fc_decode without
- * Q4FC_FLAG_STREAMK does not touch it and accepts ws = NULL. */
+ * Q4FC_FLAG_STREAMK accepts ws = NULL; given a workspace it uses it, when
+ * rows x K is large (from about 24 thousand values), to quantize the
+ * activations once in a small launch of its own in front of the FC kernel
+ * instead of inside it -- same results bit for bit, less repeated work.
+ * With Q4FC_FLAG_STREAMK, N <= 524288. */
 size_t q4fc_fc_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int group_k);
 int q4fc_fc_workspace_init(void* ws, size_t ws_bytes, q4fc_stream_t stream);
 int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,

@@ -203,6 +203,10 @@ int q4fc_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int group
 size_t q4fc_fc_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int group_k) {
     if (!valid_variant(qtype, group_k) || rows < 0 || K < 0 || N < 0) return 0;
     size_t need = decode_workspace_bytes(N);
+    if (rows <= kMaxDecodeRows) {  // room for the quantizing launch in front of the decode kernel
+        const size_t q = decode_prequant_offset() + quant_pre_bytes(rows, K, group_k);
+        if (q > need) need = q;
+    }
     if (rows > kMaxDecodeRows) {
         size_t p = prefill_workspace_bytes(rows, K, N, qtype, group_k);
         if (p > need) need = p;
@@ -239,7 +243,7 @@ int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const v
         return launch_fc_decode(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y,
                                 ldy, ws, ws_bytes, flags, static_cast<cudaStream_t>(stream));
     return launch_fc_decode_cluster(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N,
-                                    y, ldy, flags, static_cast<cudaStream_t>(stream));
+                                    y, ldy, flags, static_cast<cudaStream_t>(stream), ws, ws_bytes);
 }
 
 int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,

@@ -54,14 +54,21 @@ int launch_dequant(const uint8_t* wq, int64_t Ng, int64_t Kg, int qtype, int G, 
                    cudaStream_t s);
 int launch_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int G, float scale, int8_t* codes,
                    float* scales, float* gsums, cudaStream_t s);
+constexpr size_t kWsCounterCapacity = 64 * 1024;  // stripe counters of N <= 524288 end before the quantizer scratch
 size_t decode_workspace_bytes(int64_t N);
+size_t decode_prequant_offset();
 int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
                      int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
                      cudaStream_t s);
 // cluster form of the decode kernel (no global scratch)
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
-                             cudaStream_t s);
+                             cudaStream_t s, void* ws = nullptr, size_t ws_bytes = 0);
+// quantizing launch in front of the decode FC for large rows x K (scratch layout: quant_x.cu)
+size_t quant_pre_bytes(int64_t rows, int64_t K, int G);
+int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, bool want_isum, int8_t* codes,
+                       float* sc, bool pdl, cudaStream_t s);
+int64_t pre_quant_min_values();
 // the same kernel with outputs stored, epoch-stamped, into every rank's buffer (tp->y_peer)
 int launch_fc_decode_cluster_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                                 int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,

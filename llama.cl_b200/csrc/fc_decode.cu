@@ -413,12 +413,16 @@ constexpr int kCtasPerSm = 2;
 }  // namespace
 
 // Workspace layout (the same for every call, so that one workspace serves calls of any N):
-//   [0, 256) status | CTA partials [ctas][2][8][32] fp32 | stripe counters int[Ng]
+//   [0, 256) status | CTA partials [ctas][2][8][32] fp32 | stripe counters int[Ng] ... up to 64 KB |
+//   scratch of the quantizing launch in front of the cluster kernel (quant_x.cu), at a fixed offset so that
+//   it never lands on counters of a call with another N
 static size_t partials_bytes() {
     const DeviceInfo* di = device_info();
     const int sms = di ? di->sm_count : 256;
     return (size_t)sms * kCtasPerSm * 2 * 256 * sizeof(float);
 }
+
+size_t decode_prequant_offset() { return kWsStatusBytes + partials_bytes() + kWsCounterCapacity; }
 
 size_t decode_workspace_bytes(int64_t N) {
     const int64_t Ng = (N + 31) / 32;
@@ -433,6 +437,11 @@ int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uin
     if (!di) return Q4FC_ECUDA;
     if (Ng * Kg >= 0x7fffffffLL) {
         set_error("fc_decode: %lld blocks exceed the 2^31 limit", (long long)(Ng * Kg));
+        return Q4FC_ELIMIT;
+    }
+    if ((size_t)Ng * 4 > kWsCounterCapacity) {
+        set_error("fc_decode: the stream-K kernel takes N <= %lld; use the default decode kernel",
+                  (long long)(kWsCounterCapacity / 4 * 32));
         return Q4FC_ELIMIT;
     }
     if (ws == nullptr || ws_bytes < decode_workspace_bytes(N)) {

@@ -1,5 +1,7 @@
 // Single-GPU instantiations of the cluster decode kernel (fc_decode_cluster_impl.cuh, TP = false).
 #define Q4FC_TIMELINE_SETTER q4fc_debug_set_timeline
+#include <cstdlib>
+
 #include "fc_decode_cluster_impl.cuh"
 
 namespace q4fc {
@@ -25,10 +27,20 @@ int choose_cluster_count(int64_t Ng, int64_t nc_cap) {
     return (int)best;
 }
 
+int64_t pre_quant_min_values() {
+    static const int64_t v = [] {
+        const char* e = getenv("Q4FC_PREQUANT_MIN_VALUES");  // tuning aid: 0 = always, a huge value = never
+        if (e && *e) return (int64_t)atoll(e);
+        return kPreQuantMinValues;
+    }();
+    return v;
+}
+
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
-                             cudaStream_t s) {
-    return launch_cluster_impl<false>(x, rows, K, ldx, wq, Ng, Kg, qtype, G, N, y, ldy, flags, s, nullptr);
+                             cudaStream_t s, void* ws, size_t ws_bytes) {
+    return launch_cluster_impl<false>(x, rows, K, ldx, wq, Ng, Kg, qtype, G, N, y, ldy, flags, s, nullptr, ws,
+                                      ws_bytes);
 }
 
 }  // namespace q4fc

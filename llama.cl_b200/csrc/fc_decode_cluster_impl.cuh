@@ -87,6 +87,11 @@ struct ClusterParams {
     int slot_f;          // floats per inbox slot: 32 columns x rows (rounded up to 2)
     int inbox_slots;     // per-CTA inbox: owned stripes x cs x pmax slots
     int x_vec_ok;
+    // activations quantized beforehand by quant_x_pre_kernel (PREQ instantiations): codes [rows][xq_stride],
+    // scales and group sums [Kg][16]
+    const int8_t* xq;
+    const float* xsc;
+    int64_t xq_stride;
     // ---- N-split over several GPUs, joined by this kernel itself (world == 0: single GPU, fields unused).
     // Outputs travel as 8-byte "stamped" words: the fp32 value in the low half, the low 32 bits of the step
     // counter ("epoch") in the high half.  A 64-bit store is indivisible, so a reader that finds the current
@@ -164,7 +169,7 @@ struct Cl {
     };
 };
 
-template <int G, int QTYPE, bool SIGNED, int ROWS, bool TP>
+template <int G, int QTYPE, bool SIGNED, int ROWS, bool TP, bool PREQ>
 __global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const ClusterParams p) {
     using C = Cl<G, QTYPE>;
     constexpr int BS = C::BS;
@@ -244,8 +249,19 @@ __global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const C
     if constexpr (TP) stamp = (uint32_t)*reinterpret_cast<const volatile unsigned long long*>(p.epoch);
     Q4FC_MARK(2);
 
-    // ---- quantize this CTA's K slice of the activation rows (ops/op_fc.hpp:246-268)
-    {
+    if constexpr (PREQ) {
+        // ---- the activations were quantized by the launch before: fetch this CTA's K slice
+        const int vec_per_row = Kc * (G / 16);
+        const int8_t* src = p.xq + (int64_t)k0 * G;
+        for (int i = threadIdx.x; i < p.rows * vec_per_row; i += kCThreads) {
+            const int m = i / vec_per_row, c = i - m * vec_per_row;
+            *reinterpret_cast<uint4*>(codes + m * p.code_stride + c * 16) =
+                __ldcg(reinterpret_cast<const uint4*>(src + m * p.xq_stride) + c);
+        }
+        const float4* ssrc = reinterpret_cast<const float4*>(p.xsc) + (int64_t)k0 * 4;
+        for (int i = threadIdx.x; i < Kc * 4; i += kCThreads) reinterpret_cast<float4*>(sc)[i] = __ldcg(ssrc + i);
+    } else {
+        // ---- quantize this CTA's K slice of the activation rows (ops/op_fc.hpp:246-268)
         constexpr int SEG = G / 4;    // lanes per group
         constexpr int GPC = 128 / G;  // groups per 128-k chunk
         const int Ls = Kc * G;        // slice length per row
@@ -518,28 +534,34 @@ struct Variant {
     int max_clusters[64][4];  // [device][log2 cs], 0 = not queried yet
 };
 
-template <int G, int QTYPE, bool SIGNED, int ROWS, bool TP>
+template <int G, int QTYPE, bool SIGNED, int ROWS, bool TP, bool PREQ>
 Variant* variant_of() {
-    static Variant v = {reinterpret_cast<const void*>(&fc_decode_cluster_kernel<G, QTYPE, SIGNED, ROWS, TP>), {}, {}};
+    static Variant v = {
+        reinterpret_cast<const void*>(&fc_decode_cluster_kernel<G, QTYPE, SIGNED, ROWS, TP, PREQ>), {}, {}};
     return &v;
 }
 
+// The pre-quantized form has one instantiation per block type (its row loops run to 8 with a run-time
+// bound); the multi-GPU form always quantizes in the kernel
 template <int G, int QTYPE, bool SIGNED, bool TP>
-Variant* variant_for_rows(int rows) {
-    if (rows <= 1) return variant_of<G, QTYPE, SIGNED, 1, TP>();
-    if (rows <= 2) return variant_of<G, QTYPE, SIGNED, 2, TP>();
-    if (rows <= 4) return variant_of<G, QTYPE, SIGNED, 4, TP>();
-    return variant_of<G, QTYPE, SIGNED, 8, TP>();
+Variant* variant_for_rows(int rows, bool preq) {
+    if constexpr (!TP) {
+        if (preq) return variant_of<G, QTYPE, SIGNED, 8, TP, true>();
+    }
+    if (rows <= 1) return variant_of<G, QTYPE, SIGNED, 1, TP, false>();
+    if (rows <= 2) return variant_of<G, QTYPE, SIGNED, 2, TP, false>();
+    if (rows <= 4) return variant_of<G, QTYPE, SIGNED, 4, TP, false>();
+    return variant_of<G, QTYPE, SIGNED, 8, TP, false>();
 }
 
 template <bool TP>
-Variant* pick_variant(int qtype, int G, bool sgn, int rows) {
-    if (qtype == 1 && G == 32) return variant_for_rows<32, 1, false, TP>(rows);
-    if (qtype == 1 && G == 128) return variant_for_rows<128, 1, false, TP>(rows);
-    if (qtype == 0 && G == 32 && !sgn) return variant_for_rows<32, 0, false, TP>(rows);
-    if (qtype == 0 && G == 128 && !sgn) return variant_for_rows<128, 0, false, TP>(rows);
-    if (qtype == 0 && G == 32) return variant_for_rows<32, 0, true, TP>(rows);
-    return variant_for_rows<128, 0, true, TP>(rows);
+Variant* pick_variant(int qtype, int G, bool sgn, int rows, bool preq) {
+    if (qtype == 1 && G == 32) return variant_for_rows<32, 1, false, TP>(rows, preq);
+    if (qtype == 1 && G == 128) return variant_for_rows<128, 1, false, TP>(rows, preq);
+    if (qtype == 0 && G == 32 && !sgn) return variant_for_rows<32, 0, false, TP>(rows, preq);
+    if (qtype == 0 && G == 128 && !sgn) return variant_for_rows<128, 0, false, TP>(rows, preq);
+    if (qtype == 0 && G == 32) return variant_for_rows<32, 0, true, TP>(rows, preq);
+    return variant_for_rows<128, 0, true, TP>(rows, preq);
 }
 
 void fill_launch_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, int cs, size_t smem, bool pdl,
@@ -591,10 +613,16 @@ int max_resident_clusters(Variant* v, int dev, int cs, int log2cs, const DeviceI
 }
 
 
+// Above this many activation values (rows x K) a separate quantizing launch in front of the FC beats the
+// quantizer inside it, which every cluster runs for itself.  Needs scratch: used only when the caller's
+// workspace has room for it.
+// (pre_quant_min_values() returns kPreQuantMinValues unless the tuning variable Q4FC_PREQUANT_MIN_VALUES is set.)
+constexpr int64_t kPreQuantMinValues = 24 * 1024;
+
 template <bool TP>
 int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
                         int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags, cudaStream_t s,
-                        const q4fc_tp_site* tp) {
+                        const q4fc_tp_site* tp, void* ws = nullptr, size_t ws_bytes = 0) {
     // a rank without columns still launches nothing: its peers count only the stripes that exist
     if (rows == 0 || N == 0) return Q4FC_OK;
     const DeviceInfo* di = device_info();
@@ -616,7 +644,17 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
     }
     const bool sgn = (flags & Q4FC_FLAG_NIBBLE_SIGNED) && qtype == 0;
     const bool pdl = (flags & Q4FC_FLAG_PDL) != 0;
-    Variant* v = pick_variant<TP>(qtype, G, sgn, rows);
+    // pre-quantized input: scratch at its fixed place in the workspace, behind what the stream-K form uses
+    bool preq = false;
+    p.xq = nullptr, p.xsc = nullptr, p.xq_stride = Kg * G;
+    if (!TP && ws != nullptr && (int64_t)rows * K >= pre_quant_min_values() &&
+        (size_t)Ng * 4 <= kWsCounterCapacity && ws_bytes >= decode_prequant_offset() + quant_pre_bytes(rows, K, G)) {
+        uint8_t* base = static_cast<uint8_t*>(ws) + decode_prequant_offset();
+        p.xq = reinterpret_cast<const int8_t*>(base);
+        p.xsc = reinterpret_cast<const float*>(base + align_up((size_t)(rows * Kg * G), 256));
+        preq = true;
+    }
+    Variant* v = pick_variant<TP>(qtype, G, sgn, rows, preq);
     int dev = 0;
     Q4FC_CUDA_OK(cudaGetDevice(&dev));
     p.cs = 8;
@@ -646,9 +684,15 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
                   di->max_smem_optin);
         return Q4FC_ELIMIT;
     }
+    if (preq) {
+        if (int rc = launch_quant_x_pre(x, rows, K, ldx, G, sgn, const_cast<int8_t*>(p.xq),
+                                        const_cast<float*>(p.xsc), pdl, s))
+            return rc;
+    }
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
-    fill_launch_config(cfg, attr, p.nc * p.cs, p.cs, smem, pdl, s);
+    // behind its own quantizing launch the FC always starts early: its weight loads run beside that launch
+    fill_launch_config(cfg, attr, p.nc * p.cs, p.cs, smem, pdl || preq, s);
     void* args[] = {const_cast<ClusterParams*>(&p)};
     Q4FC_CUDA_OK(cudaLaunchKernelExC(&cfg, v->fn, args));
     return Q4FC_OK;

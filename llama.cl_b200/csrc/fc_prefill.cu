@@ -482,13 +482,17 @@ int launch_prefill_variant(const PrefillParams& p, const CUtensorMap& map, cudaS
     return Q4FC_OK;
 }
 
-// workspace: [status 256][codes rows x Kp, 256-aligned][xs rows x Kg f32][gs rows x Kg f32]
+// workspace: [status 256][what the decode kernels keep between calls: decode_prequant_offset() bytes]
+//            [codes rows x Kp, 256-aligned][xs rows x Kg f32][gs rows x Kg f32]
+// The quantized activations start where the decode path's own quantizer scratch starts: calls on one
+// workspace are ordered, so the two can share that space, and neither lands on the stream-K stripe
+// counters, which must stay zero between calls.
 struct WsLayout {
     size_t codes, xs, gs, total;
 };
 WsLayout ws_layout(int64_t rows, int64_t Kg, int G) {
     WsLayout l;
-    l.codes = kWsStatusBytes;
+    l.codes = decode_prequant_offset();
     l.xs = align_up(l.codes + (size_t)rows * Kg * G, 256);
     l.gs = align_up(l.xs + (size_t)rows * Kg * 4, 256);
     l.total = align_up(l.gs + (size_t)rows * Kg * 4, 256);

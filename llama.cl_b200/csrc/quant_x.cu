@@ -109,7 +109,121 @@ __global__ void __launch_bounds__(kQxWarps * 32) quant_x_kernel(const float* __r
     }
 }
 
+// Quantizer in front of the decode FC when rows x K is large.  The decode kernel normally quantizes the
+// activations itself, every cluster for itself; beyond a few tens of thousands of values that repeated work
+// costs more than one extra small launch.  One warp owns 128 consecutive k of ONE row, so the whole input is
+// spread over hundreds of warps and the kernel is a single short latency chain.  Codes and scales follow
+// the same rules as quant_x_kernel; the group sums are formed in exactly the order of the decode kernel's
+// own quantizer (four values per lane in k order, then a butterfly over the group's lanes), so the FC
+// result does not depend on which of the two quantized the input.
+//   codes: int8 [rows][Kg*G];   sc: fp32 [Kg][16], entry 2*m = scale d of row m, entry 2*m + 1 = group sum
+//   (or, for the signed-nibble Q4_0 form, the bits of the integer 8 * sum of codes).
+template <int G>
+__global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restrict__ x, int rows, int64_t K,
+                                                          int64_t ldx, int64_t Kg, int vec_ok, int want_isum,
+                                                          int8_t* __restrict__ codes, float* __restrict__ sc) {
+    constexpr int SEG = G / 4;
+    constexpr int GPC = 128 / G;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t chunks = (Kg * G + 127) / 128;
+    const int64_t unit = (int64_t)blockIdx.x * 4 + warp;
+    pdl_launch_dependents();
+    if (unit >= chunks * rows) return;
+    const int64_t c = unit / rows;
+    const int m = (int)(unit - c * rows);
+    const int64_t k = c * 128 + lane * 4;
+    const int64_t kb = c * GPC + lane / SEG;
+    const bool exists = kb < Kg;
+    const int len = exists ? (int)min((int64_t)G, K - kb * G) : 0;
+    const int body = len & ~7;
+    const int e0 = (lane % SEG) * 4;
+    pdl_wait_prior_grid();  // the activations may come from the kernel before
+
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* src = x + m * ldx + k;
+    if (vec_ok && k + 4 <= K) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(src));
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (k + j < K) v[j] = __ldcg(src + j);
+    }
+    float amax = 0.0f, fsum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        if (e0 + j < len) {
+            amax = fmaxf(amax, fabsf(v[j]));
+            fsum += v[j];
+        }
+#pragma unroll
+    for (int off = SEG / 2; off > 0; off >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        fsum += __shfl_xor_sync(0xffffffffu, fsum, off);
+    }
+    const float d = div_const_rn(amax, 127.0f, 1.0f / 127.0f);
+    const float id = inv_or_zero(d);
+    uint32_t packed = 0;
+    int isum = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        int q = 0;
+        if (e0 + j < len) {
+            const float t = __fmul_rn(v[j], id);
+            if (e0 + j < body) {
+                q = __float2int_rn(t);
+            } else {
+                const float h = __int_as_float((__float_as_int(t) & 0x80000000) | 0x3F000000);
+                q = __float2int_rz(__fadd_rz(t, h));
+            }
+            q = sat8(q);
+        }
+        isum += q;
+        packed |= (uint32_t)(q & 0xFF) << (8 * j);
+    }
+    if (want_isum) {
+#pragma unroll
+        for (int off = SEG / 2; off > 0; off >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, off);
+    }
+    if (exists) {
+        *reinterpret_cast<uint32_t*>(codes + m * (Kg * G) + k) = packed;
+        if (e0 == 0) {
+            sc[kb * 16 + m * 2 + 0] = d;
+            sc[kb * 16 + m * 2 + 1] = want_isum ? __int_as_float(8 * isum) : fsum;
+        }
+    }
+}
+
 }  // namespace
+
+size_t quant_pre_bytes(int64_t rows, int64_t K, int G) {
+    const int64_t Kg = (K + G - 1) / G;
+    return align_up((size_t)(rows * Kg * G), 256) + align_up((size_t)Kg * 16 * sizeof(float), 256);
+}
+
+int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, bool want_isum, int8_t* codes,
+                       float* sc, bool pdl, cudaStream_t s) {
+    const int64_t Kg = (K + G - 1) / G;
+    const int64_t chunks = (Kg * G + 127) / 128;
+    const int64_t grid = (chunks * rows + 3) / 4;
+    const int vec_ok = (K % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(128);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    if (G == 32)
+        Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_kernel<32>, x, rows, K, ldx, Kg, vec_ok, (int)want_isum, codes,
+                                        sc));
+    else
+        Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_kernel<128>, x, rows, K, ldx, Kg, vec_ok, (int)want_isum,
+                                        codes, sc));
+    return Q4FC_OK;
+}
 
 int launch_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int G, float scale, int8_t* codes,
                    float* scales, float* gsums, cudaStream_t s) {

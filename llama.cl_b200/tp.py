@@ -338,3 +338,61 @@ class FusedTPLinearQ4:
             self.n1 - self.n0, self.ldy, C.byref(self._site(stamped)), self.flags, self.arena._stream()),
             "fc_decode_tp")
         return StampedOutput(self, B, M)
+
+
+class HostFusedFC:
+    """Host buffers in, host buffers out, over an N-split FC (the multi-GPU counterpart of ``host.HostFC``).
+
+    Every rank makes the same call with the same activations.  Per call: copy in from pinned host memory,
+    step barrier, the fused FC, unpacking of the gathered output, copy out to pinned host memory -- captured
+    once per row count into a CUDA graph and replayed.  The FC is a schedule of its own, so calls need no
+    coordination with other layers; ``stream`` defaults to a stream of its own."""
+
+    def __init__(self, arena: TPArena, wq_shard: torch.Tensor, N: int, max_rows: int = 8, graph: bool = True,
+                 stream: "torch.cuda.Stream | None" = None, **layer_kwargs) -> None:
+        self.schedule = TPSchedule(arena)
+        self.layer = FusedTPLinearQ4(self.schedule, wq_shard, N, max_rows=max_rows, **layer_kwargs)
+        dev = arena.device
+        self.N, self.K, self.max_rows = int(N), self.layer.Kg * self.layer.group_k, int(max_rows)
+        self.stream = stream if stream is not None else torch.cuda.Stream(dev)
+        self._x_dev = torch.empty((1, max_rows, self.K), dtype=torch.float32, device=dev)
+        self._y_dev = torch.empty((1, max_rows, self.N), dtype=torch.float32, device=dev)
+        self._x_host = torch.empty((1, max_rows, self.K), dtype=torch.float32).pin_memory()
+        self._y_host = torch.empty((1, max_rows, self.N), dtype=torch.float32).pin_memory()
+        self.use_graph = bool(graph)
+        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+
+    def x_staging(self, M: int) -> torch.Tensor:
+        return self._x_host[:, :M]
+
+    def _enqueue(self, M: int) -> None:
+        xd = self._x_dev[:, :M]
+        xd.copy_(self._x_host[:, :M], non_blocking=True)
+        self.schedule.step_begin()
+        yd = self.layer(xd).tensor(out=self._y_dev[:, :M])  # the leading dimension is 1: a contiguous slice
+        self._y_host[:, :M].copy_(yd, non_blocking=True)
+
+    def __call__(self, x_host: torch.Tensor, sync: bool = True) -> torch.Tensor:
+        M = x_host.shape[1]
+        if M > self.max_rows or x_host.shape[2] != self.K:
+            raise RuntimeError(f"HostFusedFC: input {tuple(x_host.shape)} does not fit [1, <={self.max_rows}, {self.K}]")
+        stage = self._x_host[:, :M]
+        if x_host.data_ptr() != stage.data_ptr():
+            stage.copy_(x_host)
+        with torch.cuda.stream(self.stream):
+            if self.use_graph:
+                g = self._graphs.get(M)
+                if g is None:
+                    # eager once (every rank does: the step barrier pairs up), then capture
+                    self._enqueue(M)
+                    self.stream.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        self._enqueue(M)
+                    self._graphs[M] = g
+                g.replay()
+            else:
+                self._enqueue(M)
+        if sync:
+            self.stream.synchronize()
+        return self._y_host[:, :M]

@@ -222,10 +222,14 @@ def test_fc_repeatable_and_workspace_reuse(pkg, oracle):
         y0 = pkg.llmops.fc_Q4A(x, wq, 4096, path=path)
         for _ in range(5):
             assert torch.equal(pkg.llmops.fc_Q4A(x, wq, 4096, path=path), y0)
-    ws = pkg.llmops.fc_workspace(4, 4096, 4096, 1, 128, x.device)
+    # an explicit workspace, reused by calls of both kernels one after the other: every call must leave it
+    # ready for the next (the stream-K kernel returns its stripe counters to zero), or results would drift
+    ws = pkg.llmops.Workspace(pkg._cabi.lib().q4fc_fc_workspace_bytes(4, 4096, 4096, 1, 128), x.device)
+    for i in range(6):
+        path = ("streamk", "decode")[i & 1]
+        assert torch.equal(pkg.llmops.fc_Q4A(x, wq, 4096, path=path, workspace=ws),
+                           pkg.llmops.fc_Q4A(x, wq, 4096, path=path))
     ws.check()
-    counters = ws.buf[ws.nbytes - 4 * 128:].view(torch.int32)   # the counters close the workspace
-    assert int(counters.abs().sum().item()) == 0, "stripe counters must return to zero"
 
 
 def test_fc_workspace_shared_between_shapes(pkg, oracle):
@@ -434,3 +438,36 @@ def test_host_fc_graph_and_streams(lib_built):
             assert torch.equal(y, pkg.llmops.fc_Q4A((x * 2).to(dev), wq, N, path="decode").cpu())
     with pytest.raises(RuntimeError):
         hg(torch.zeros(1, 9, K))
+
+
+@pytest.mark.parametrize("qname,q,G,signed", [("q4_1", 1, 128, False), ("q4_1", 1, 32, False), ("q4_0", 0, 32, False),
+                                              ("q4_0", 0, 128, True)])
+def test_decode_prequantized_path_equals_fused_quantizer(lib_built, qname, q, G, signed):
+    """For large rows x K the decode entry point quantizes the activations in a launch of its own (when the
+    workspace has room for the codes) instead of inside the FC kernel.  Both quantizers follow the same
+    rules in the same order, so the outputs are bit-identical; without a workspace the fused one runs."""
+    import llama_cl_b200 as pkg
+
+    L = pkg._cabi.lib()
+    g = torch.Generator().manual_seed(77)
+    s = torch.cuda.current_stream().cuda_stream
+    flags = 1 if signed else 0
+    for (N, K, rows) in [(4096, 4096, 8), (1000, 11008, 3), (640, 3080, 8), (96, 4096, 6)]:
+        W = (torch.randn(N, K, generator=g) * 0.02).cuda()
+        wq = pkg.llmops.offline_FC_quant_Q4A(W, qtype=qname, group_k=G)
+        Ng, Kg, _ = wq.shape
+        x = torch.randn(1, rows, K, generator=g).cuda()
+        nbytes = int(L.q4fc_fc_workspace_bytes(rows, K, N, q, G))
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        outs = []
+        for w in (None, ws, ws):  # the second pass over the same scratch finds it used
+            y = torch.full((1, rows, N), float("nan"), device="cuda")
+            rc = L.q4fc_fc_decode(x.data_ptr(), rows, K, K, wq.data_ptr(), Ng, Kg, q, G, N, y.data_ptr(), N,
+                                  w.data_ptr() if w is not None else None, nbytes if w is not None else 0, flags, s)
+            assert rc == 0, L.q4fc_last_error()
+            outs.append(y)
+        torch.cuda.synchronize()
+        assert rows * K >= 24 * 1024  # the sizes above are meant to take the separate launch
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), (N, K, rows)
+        want = pkg.llmops.fc_Q4A(x, wq, N, path="streamk", nibble_signed=signed)
+        assert torch.allclose(outs[1], want, rtol=1e-3, atol=1e-4)

@@ -158,6 +158,15 @@ def _fused_worker(rank, world, initfile, result_q):
             torch.cuda.synchronize()
             want = pkg.llmops.fc_Q4A(xg, full["q"], H)
             expect(torch.allclose(y, want, rtol=1e-3, atol=1e-4), f"solo schedule step {step}")
+        # host buffers in and out over the N-split FC, as a replayed graph, two row counts, fresh inputs
+        hf = tp.HostFusedFC(arena, tp.shard_packed(full["up"], world, rank), I, max_rows=4, pdl=True)
+        for step in range(3):
+            for M in (1, 4):
+                g = torch.Generator().manual_seed(300 + 10 * step + M)
+                xh = torch.randn(1, M, H, generator=g)
+                y = hf(xh).clone()
+                want = pkg.llmops.fc_Q4A(xh.to(dev), full["up"], I).cpu()
+                expect(torch.allclose(y, want, rtol=1e-3, atol=1e-4), f"HostFusedFC step {step} M={M}")
         outs = chain(xg)  # and the first schedule is undisturbed by it
         torch.cuda.synchronize()
         verify(xg, outs, "after the solo schedule")
