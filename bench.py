@@ -293,7 +293,7 @@ def our_arm(args) -> None:
             load[i] += packed_bytes(c["K"], c["n_local"]) / 5e12 + 4e-6 * (1 + c["M"] / 8)
         return plan
 
-    def run_calls(cs, pdl: bool = True, wsp=None) -> None:
+    def run_calls(cs, pdl: bool = True, wsp=None, side_by_side: bool = False) -> None:
         outs = []
         wsp = ws if wsp is None else wsp
         for c in cs:
@@ -302,7 +302,8 @@ def our_arm(args) -> None:
             elif distributed:
                 c["layer"](c["x"])
             else:
-                pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=wsp, pdl=pdl, path="decode")
+                pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=wsp, pdl=pdl, path="decode",
+                                  prequant=side_by_side)
         # fused: unpack to plain fp32 behind the lane's FCs (each unpacking kernel waits for the other ranks'
         # columns), so that the step ends when every rank holds every full output
         for c, o in outs:
@@ -321,7 +322,7 @@ def our_arm(args) -> None:
         for st, cs, wsp in zip(lane_streams, deal(lanes), lane_ws):
             st.wait_event(start)
             with torch.cuda.stream(st):
-                run_calls(cs, wsp=wsp)
+                run_calls(cs, wsp=wsp, side_by_side=True)
         for st in lane_streams[:lanes]:
             cur.wait_stream(st)
 

@@ -65,7 +65,13 @@ enum {
      * per CTA, partial sums through the workspace) instead of the default
      * cluster kernel (partial sums through distributed shared memory, no
      * workspace needed).  Same results within rounding of the fp32 sums. */
-    Q4FC_FLAG_STREAMK = 4u
+    Q4FC_FLAG_STREAMK = 4u,
+    /* q4fc_fc_decode with a workspace: always quantize the activations in a small launch of their own in
+     * front of the FC kernel (by default only for large rows x K).  The FC kernel otherwise quantizes
+     * them itself, every cluster its own copy: the shortest path for one call at a time, but repeated
+     * work that competes for the SMs when several FCs run side by side on different streams.  Same
+     * results bit for bit. */
+    Q4FC_FLAG_PREQUANT = 8u
 };
 
 int q4fc_version(void);
@@ -113,7 +119,7 @@ int q4fc_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int group
  * the kernels leave it ready for the next call.  Calls that may overlap on
  * the GPU need separate workspaces.  q4fc_fc_decode without
  * Q4FC_FLAG_STREAMK accepts ws = NULL; given a workspace it uses it, when
- * rows x K is large (from about 24 thousand values), to quantize the
+ * rows x K is large (from about 40 thousand values), to quantize the
  * activations once in a small launch of its own in front of the FC kernel
  * instead of inside it -- same results bit for bit, less repeated work.
  * With Q4FC_FLAG_STREAMK, N <= 524288. */

@@ -15,6 +15,7 @@ Q4_0, Q4_1 = 0, 1
 FLAG_NIBBLE_SIGNED = 1
 FLAG_PDL = 2
 FLAG_STREAMK = 4
+FLAG_PREQUANT = 8
 
 # every symbol declared in include/q4fc_b200.h
 SYMBOLS = (

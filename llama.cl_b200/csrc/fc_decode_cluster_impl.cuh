@@ -617,7 +617,10 @@ int max_resident_clusters(Variant* v, int dev, int cs, int log2cs, const DeviceI
 // quantizer inside it, which every cluster runs for itself.  Needs scratch: used only when the caller's
 // workspace has room for it.
 // (pre_quant_min_values() returns kPreQuantMinValues unless the tuning variable Q4FC_PREQUANT_MIN_VALUES is set.)
-constexpr int64_t kPreQuantMinValues = 24 * 1024;
+// Measured on Llama-7B shapes: it pays when the per-CTA share of the quantization (rows x K / 8) is the long
+// pole -- K = 11008 at 4 and 8 rows (15 -> 13 us, 21 -> 14 us per call) -- and not at K = 4096, where for wide
+// outputs the extra launch competes with the weight stream the FC kernel has already requested.
+constexpr int64_t kPreQuantMinValues = 40 * 1024;
 
 template <bool TP>
 int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
@@ -647,7 +650,7 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
     // pre-quantized input: scratch at its fixed place in the workspace, behind what the stream-K form uses
     bool preq = false;
     p.xq = nullptr, p.xsc = nullptr, p.xq_stride = Kg * G;
-    if (!TP && ws != nullptr && (int64_t)rows * K >= pre_quant_min_values() &&
+    if (!TP && ws != nullptr && ((flags & Q4FC_FLAG_PREQUANT) || (int64_t)rows * K >= pre_quant_min_values()) &&
         (size_t)Ng * 4 <= kWsCounterCapacity && ws_bytes >= decode_prequant_offset() + quant_pre_bytes(rows, K, G)) {
         uint8_t* base = static_cast<uint8_t*>(ws) + decode_prequant_offset();
         p.xq = reinterpret_cast<const int8_t*>(base);

@@ -121,14 +121,17 @@ __global__ void __launch_bounds__(kQxWarps * 32) quant_x_kernel(const float* __r
 template <int G>
 __global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restrict__ x, int rows, int64_t K,
                                                           int64_t ldx, int64_t Kg, int vec_ok, int want_isum,
-                                                          int8_t* __restrict__ codes, float* __restrict__ sc) {
+                                                          int early_release, int8_t* __restrict__ codes,
+                                                          float* __restrict__ sc) {
     constexpr int SEG = G / 4;
     constexpr int GPC = 128 / G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t chunks = (Kg * G + 127) / 128;
     const int64_t unit = (int64_t)blockIdx.x * 4 + warp;
-    pdl_launch_dependents();
-    if (unit >= chunks * rows) return;
+    // In a chain of programmatic launches the FC kernel behind this one should start as early as it can:
+    // its start-up then runs beside the FC before.
+    if (early_release) pdl_launch_dependents();
+    if (unit >= chunks * rows) return;  // (an exited warp counts as having released the dependent launch)
     const int64_t c = unit / rows;
     const int m = (int)(unit - c * rows);
     const int64_t k = c * 128 + lane * 4;
@@ -156,6 +159,10 @@ __global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restric
             amax = fmaxf(amax, fabsf(v[j]));
             fsum += v[j];
         }
+    // Otherwise the FC kernel behind this launch is released only now, with this warp's activations in
+    // registers: its first act is to request megabytes of weights, and these few loads would queue behind
+    // that stream.
+    if (!early_release) pdl_launch_dependents();
 #pragma unroll
     for (int off = SEG / 2; off > 0; off >>= 1) {
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
@@ -217,11 +224,11 @@ int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, 
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     if (G == 32)
-        Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_kernel<32>, x, rows, K, ldx, Kg, vec_ok, (int)want_isum, codes,
-                                        sc));
+        Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_kernel<32>, x, rows, K, ldx, Kg, vec_ok, (int)want_isum,
+                                        (int)pdl, codes, sc));
     else
         Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_kernel<128>, x, rows, K, ldx, Kg, vec_ok, (int)want_isum,
-                                        codes, sc));
+                                        (int)pdl, codes, sc));
     return Q4FC_OK;
 }
 

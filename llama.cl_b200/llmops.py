@@ -140,13 +140,15 @@ def FC_dynamic_quantize_x(input: torch.Tensor, group_k: int, scale: float = 1.0)
 
 def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_signed: bool = False,
            out: torch.Tensor | None = None, workspace: Workspace | None = None, pdl: bool = False,
-           path: str = "auto") -> torch.Tensor:
+           path: str = "auto", prequant: bool = False) -> torch.Tensor:
     """``y[b, m, :N] = quantized(input[b, m]) . W`` (ops/op_fc.hpp:286-426).
 
     input fp32 ``[B, M, K]``, wei_quantized int8 ``[Ng, Kg, block_bytes]`` ->
     fp32 ``[B, M, N]``.  ``path``: "auto" (decode kernel for B*M <= 8, else
     the prefill kernel), "decode", "streamk" (the decode kernel that reduces
-    through the workspace) or "prefill"."""
+    through the workspace) or "prefill".  ``prequant=True`` (decode kernel): quantize the activations in a
+    small launch of their own whatever the size -- less total work when several FCs run side by side on
+    different streams; by default that happens only for large rows x K."""
     _require_cuda(input, "input", torch.float32, 3)
     _require_cuda(wei_quantized, "wei_quantized", torch.int8, 3)
     if wei_quantized.device != input.device:
@@ -167,6 +169,8 @@ def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_s
     flags = (FLAG_NIBBLE_SIGNED if nibble_signed else 0) | (FLAG_PDL if pdl else 0)
     if path == "streamk":
         flags |= FLAG_STREAMK
+    if prequant:
+        flags |= _cabi.FLAG_PREQUANT
     L = _cabi.lib()
     fn = {"auto": L.q4fc_fc, "decode": L.q4fc_fc_decode, "streamk": L.q4fc_fc_decode,
           "prefill": L.q4fc_fc_prefill}[path]

@@ -452,7 +452,7 @@ def test_decode_prequantized_path_equals_fused_quantizer(lib_built, qname, q, G,
     g = torch.Generator().manual_seed(77)
     s = torch.cuda.current_stream().cuda_stream
     flags = 1 if signed else 0
-    for (N, K, rows) in [(4096, 4096, 8), (1000, 11008, 3), (640, 3080, 8), (96, 4096, 6)]:
+    for (N, K, rows) in [(4096, 11008, 8), (1000, 11008, 4), (640, 6152, 8), (96, 8192, 6)]:
         W = (torch.randn(N, K, generator=g) * 0.02).cuda()
         wq = pkg.llmops.offline_FC_quant_Q4A(W, qtype=qname, group_k=G)
         Ng, Kg, _ = wq.shape
@@ -467,7 +467,7 @@ def test_decode_prequantized_path_equals_fused_quantizer(lib_built, qname, q, G,
             assert rc == 0, L.q4fc_last_error()
             outs.append(y)
         torch.cuda.synchronize()
-        assert rows * K >= 24 * 1024  # the sizes above are meant to take the separate launch
+        assert rows * K >= 40 * 1024  # the sizes above are meant to take the separate launch
         assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), (N, K, rows)
         want = pkg.llmops.fc_Q4A(x, wq, N, path="streamk", nibble_signed=signed)
         assert torch.allclose(outs[1], want, rtol=1e-3, atol=1e-4)
