@@ -17,8 +17,9 @@ value  packed weight GB/s (packed bytes / time, 1 GB = 1e9 B: the reference's
        are independent, so the graph runs them on --lanes parallel branches
        (default 4); the roofline figure is taken from a second timed pass with
        the same launches strictly one after the other.
-e2e    the same metric through the host-buffer API (HostFC): activations
-       copied from pinned host memory, result copied back, every call.
+e2e    the same metric through the host-buffer API (HostFC / HostFCGroup):
+       activations copied from pinned host memory, results copied back to
+       pinned host memory, every call, the step's calls submitted together.
 
 With --gpus N > 1 every FC weight is split along N over the ranks (strong
 scaling: the job is the same sweep, each rank streams 1/N of every weight).
@@ -415,25 +416,26 @@ def our_arm(args) -> None:
                 hosts.append(None)
             else:
                 hosts.append(HostFC(c["wq"], c["N"], max_rows=8, workspace=lane_ws[len(hosts) % n_lanes],
-                                    path="decode", stream=lane_streams[len(hosts) % n_lanes]))
+                                    path="decode", prequant=n_lanes > 1, stream=lane_streams[len(hosts) % n_lanes]))
         # the activations sit in the pinned input buffer of the call's host front end
         xs_host = [c["x"].cpu().pin_memory() if h is None else h.x_staging(c["M"]).copy_(c["x"].cpu())
                    for c, h in zip(calls, hosts)]
         ys_host = [torch.empty((1, c["M"], c["N"]), dtype=torch.float32).pin_memory() for c in calls]
 
+        from llama_cl_b200.host import HostFCGroup
+
+        group = HostFCGroup(hosts) if all(h is not None for h in hosts) else None
+
         def step_e2e() -> None:
-            for c, h, xh, yh in zip(calls, hosts, xs_host, ys_host):
-                if fused:
-                    h(xh, sync=False)
-                elif distributed:
-                    c["x"].copy_(xh, non_blocking=True)
-                    y = c["layer"](c["x"])
-                    yh.copy_(y, non_blocking=True)
-                else:
-                    h(xh, sync=False)
+            if group is not None:
+                # the step's 16 calls as one submission: copies in, kernels, copies out on the lanes' streams
+                group(xs_host, sync=True)
+                return
+            for c, xh, yh in zip(calls, xs_host, ys_host):  # NCCL form: eager, call by call
+                c["x"].copy_(xh, non_blocking=True)
+                y = c["layer"](c["x"])
+                yh.copy_(y, non_blocking=True)
             torch.cuda.current_stream(dev).synchronize()
-            for st in lane_streams:
-                st.synchronize()
 
         n_e2e = max(3, min(args.steps, 200))
         for _ in range(3):
@@ -639,6 +641,16 @@ def our_arm(args) -> None:
             check = bool(np.allclose(mine, want, rtol=1e-3, atol=1e-4)) and ranks_agree
 
     tp_status = arena.status() if fused else 0  # non-zero: a bounded wait on another rank ran out
+    # this library's kernels per timed step: the FC kernel of every call, plus -- side by side on one GPU --
+    # the quantizing launch in front of each, or -- N-split -- the step barrier and one unpacking kernel per call
+    if fused:
+        launches_per_step = 2 * len(calls) + 1
+    elif distributed:
+        launches_per_step = len(calls)
+    elif n_lanes > 1:
+        launches_per_step = 2 * len(calls)
+    else:
+        launches_per_step = len(calls) + sum(1 for c in calls if c["M"] * c["K"] >= 40 * 1024)
     if rank == 0:
         peak, peak_kind = load_peaks()
         # per launch: the step's algorithmic bytes and time divided by its 16 launches
@@ -671,7 +683,7 @@ def our_arm(args) -> None:
                            launch=(f"cuda graph of one step, the 16 independent calls on {n_lanes} parallel branches"
                                    if graphed else "eager"),
                            lanes=n_lanes),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": (len(calls) * (2 if fused else 1) + (1 if fused else 0)) * args.steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
             **({"tp_status": tp_status} if fused else {}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,

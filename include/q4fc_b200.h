@@ -187,6 +187,8 @@ typedef struct q4fc_tp_site {
     int* status;                     /* local int, set non-zero when a bounded wait ran out */
 } q4fc_tp_site;
 
+/* sizeof(q4fc_tp_site) as the library was built: bindings that mirror the struct check theirs against it */
+size_t q4fc_tp_site_bytes(void);
 int q4fc_tp_arena_create(size_t bytes, void** base, void* ipc_handle_64);
 int q4fc_tp_arena_open(const void* ipc_handle_64, void** peer_base);
 int q4fc_tp_arena_close(void* peer_base);

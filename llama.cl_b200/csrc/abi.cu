@@ -266,6 +266,8 @@ int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq
     return q4fc_fc_prefill(x, rows, K, ldx, wq, Ng, Kg, qtype, group_k, N, y, ldy, ws, ws_bytes, flags, stream);
 }
 
+size_t q4fc_tp_site_bytes(void) { return sizeof(q4fc_tp_site); }
+
 int q4fc_tp_arena_create(size_t bytes, void** base, void* ipc_handle_64) {
     if (!base || !ipc_handle_64 || bytes == 0) {
         set_error("tp_arena_create: null argument or zero size");

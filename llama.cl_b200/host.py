@@ -91,3 +91,60 @@ class HostFC:
 
     def d2h_bytes(self, M: int) -> int:
         return 4 * M * self.N
+
+
+class HostFCGroup:
+    """Several independent host-buffer FCs submitted together: ``ys = group(xs)``.
+
+    ``members`` are ``HostFC`` objects (or ``tp.HostFusedFC``), each with its own staging buffers and stream.
+    One call copies every member's activations in, runs every FC and copies every result out as ONE replayed
+    CUDA graph whose branches are the members' streams, so the per-call cost on the CPU is paid once for the
+    whole group and copies of one member overlap kernels of another.  The graph is captured once per tuple of
+    row counts.  Returns the members' pinned output buffers, valid after ``sync`` (default: waited for here)."""
+
+    def __init__(self, members) -> None:
+        self.members = list(members)
+        if not self.members:
+            raise RuntimeError("HostFCGroup: no members")
+        dev = self.members[0].device if hasattr(self.members[0], "device") else self.members[0].stream.device
+        self.device = dev
+        self.stream = torch.cuda.Stream(dev)
+        self._graphs: dict = {}
+
+    def _enqueue(self, Ms) -> None:
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        seen = []
+        for h, M in zip(self.members, Ms):
+            if h.stream not in seen:
+                h.stream.wait_event(start)
+                seen.append(h.stream)
+            with torch.cuda.stream(h.stream):
+                h._enqueue(M)
+        for st in seen:
+            cur.wait_stream(st)
+
+    def __call__(self, xs, sync: bool = True):
+        if len(xs) != len(self.members):
+            raise RuntimeError(f"HostFCGroup: {len(xs)} inputs for {len(self.members)} members")
+        Ms = tuple(int(x.shape[1]) for x in xs)
+        for h, x, M in zip(self.members, xs, Ms):
+            if M > h.max_rows or x.shape[2] != h.K:
+                raise RuntimeError(f"HostFCGroup: input {tuple(x.shape)} does not fit [1, <={h.max_rows}, {h.K}]")
+            stage = h.x_staging(M)
+            if x.data_ptr() != stage.data_ptr():
+                stage.copy_(x)
+        with torch.cuda.stream(self.stream):
+            g = self._graphs.get(Ms)
+            if g is None:
+                self._enqueue(Ms)  # eager once: lazy look-ups and kernel attributes happen outside the capture
+                torch.cuda.synchronize(self.device)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.stream):
+                    self._enqueue(Ms)
+                self._graphs[Ms] = g
+            g.replay()
+        if sync:
+            self.stream.synchronize()
+        return [h._y_host[:, :M] for h, M in zip(self.members, Ms)]

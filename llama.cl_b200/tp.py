@@ -353,6 +353,7 @@ class HostFusedFC:
         self.schedule = TPSchedule(arena)
         self.layer = FusedTPLinearQ4(self.schedule, wq_shard, N, max_rows=max_rows, **layer_kwargs)
         dev = arena.device
+        self.device = dev
         self.N, self.K, self.max_rows = int(N), self.layer.Kg * self.layer.group_k, int(max_rows)
         self.stream = stream if stream is not None else torch.cuda.Stream(dev)
         self._x_dev = torch.empty((1, max_rows, self.K), dtype=torch.float32, device=dev)

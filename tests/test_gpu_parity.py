@@ -471,3 +471,28 @@ def test_decode_prequantized_path_equals_fused_quantizer(lib_built, qname, q, G,
         assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), (N, K, rows)
         want = pkg.llmops.fc_Q4A(x, wq, N, path="streamk", nibble_signed=signed)
         assert torch.allclose(outs[1], want, rtol=1e-3, atol=1e-4)
+
+
+def test_host_fc_group(lib_built):
+    """Several host-buffer FCs submitted as one replayed graph over their own streams: same bytes as the
+    one-by-one calls, for changing inputs and for a second combination of row counts."""
+    import llama_cl_b200 as pkg
+    from llama_cl_b200.host import HostFC, HostFCGroup
+
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(6)
+    shapes = [(1000, 1024), (512, 2048), (96, 1024)]
+    wqs = [pkg.llmops.offline_FC_quant_Q4A((torch.randn(N, K, generator=g) * 0.02).to(dev), qtype="q4_1", group_k=128)
+           for N, K in shapes]
+    streams = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
+    members = [HostFC(wq, N, max_rows=8, path="decode", stream=streams[i % 2],
+                      workspace=pkg.llmops.Workspace(pkg._cabi.lib().q4fc_fc_workspace_bytes(8, K, N, 1, 128), dev))
+               for i, (wq, (N, K)) in enumerate(zip(wqs, shapes))]
+    group = HostFCGroup(members)
+    for Ms in [(1, 4, 8), (1, 4, 8), (2, 2, 1), (1, 4, 8)]:
+        xs = [torch.randn(1, M, K, generator=g) for M, (N, K) in zip(Ms, shapes)]
+        ys = [y.clone() for y in group(xs)]
+        for y, x, wq, (N, K) in zip(ys, xs, wqs, shapes):
+            assert torch.equal(y, pkg.llmops.fc_Q4A(x.to(dev), wq, N, path="decode").cpu())
+    with pytest.raises(RuntimeError):
+        group([torch.zeros(1, 1, 1024)])
