@@ -478,11 +478,23 @@ def our_arm(args) -> None:
                 return make_layer(tok_sched, wq_, N, max_rows=1), wq_.numel()
             if distributed:
                 return make_layer(None, wq_, N), wq_.numel()
-            out = torch.empty((1, 1, N), device=dev, dtype=torch.float32)
-            return (lambda x_, wq_=wq_, N=N, out=out: pkg.llmops.fc_Q4A(
-                x_, wq_, N, out=out, workspace=stream_ws(), pdl=True, path="decode")), wq_.numel()
+            return _LocalFC(wq_, N), wq_.numel()
 
         ws_of_stream: dict = {}
+
+        class _LocalFC:
+            """One FC of the stack on this GPU: on fp32 activations, or on activations quantized beforehand."""
+
+            def __init__(self, wq_, N_):
+                self.wq, self.N = wq_, N_
+                self.out = torch.empty((1, 1, N_), device=dev, dtype=torch.float32)
+
+            def __call__(self, x_):
+                return pkg.llmops.fc_Q4A(x_, self.wq, self.N, out=self.out, workspace=stream_ws(), pdl=True,
+                                         path="decode")
+
+            def q8(self, xq_):
+                return pkg.llmops.fc_Q4A_q8(xq_, self.wq, self.N, out=self.out, pdl=True)
 
         def stream_ws():
             """One workspace per stream: FCs running side by side must not share scratch."""
@@ -539,18 +551,21 @@ def our_arm(args) -> None:
             if fused:
                 y.tensor(out=logits)  # the token is done when every rank holds the whole logits row
 
-        run_token, tok_graphed = capture(token)
-        n_tok = max(3, min(args.steps, 100))
-        for _ in range(3):
-            run_token()
-        barrier()
-        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a0.record()
-        for _ in range(n_tok):
-            run_token()
-        a1.record()
-        barrier()
-        ms_tok = a0.elapsed_time(a1)
+        def time_token(fn):
+            run, graphed_ = capture(fn)
+            n_ = max(3, min(args.steps, 100))
+            for _ in range(3):
+                run()
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(n_):
+                run()
+            a1.record()
+            barrier()
+            return a0.elapsed_time(a1), n_, graphed_
+
+        ms_tok, n_tok, tok_graphed = time_token(token)
         if distributed:
             t = torch.tensor([ms_tok], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -563,6 +578,25 @@ def our_arm(args) -> None:
                  "launch": "cuda graph of one token" if tok_graphed else "eager",
                  "what": "Q4_1 group-128 FC stack of a random-init 32-layer Llama-7B (hidden 4096, intermediate "
                          "11008, vocab 32000 lm_head), batch 1; FC kernels only"}
+        if not distributed:
+            # the same pass with every shared input quantized once (q/k/v read one quantized copy, gate/up
+            # another) instead of once per FC as the reference does
+            xq_a = pkg.llmops.QuantizedActivations(1, 1, H, GROUP_K, False, dev)
+            xq_b = pkg.llmops.QuantizedActivations(1, 1, H, GROUP_K, False, dev)
+
+            def token_quantize_once() -> None:
+                h = h0
+                for f in layers:
+                    xa = pkg.llmops.quantize_activations(h, GROUP_K, pdl=True, out=xq_a)
+                    q, _, _ = fork([f["q"].q8, f["k"].q8, f["v"].q8], xa)
+                    o = f["o"](q)
+                    xb = pkg.llmops.quantize_activations(o, GROUP_K, pdl=True, out=xq_b)
+                    g_, _ = fork([f["gate"].q8, f["up"].q8], xb)
+                    h = f["down"](g_)
+                lm_head(h)
+
+            ms_once, n_once, _ = time_token(token_quantize_once)
+            stack["ms_per_token_quantize_once"] = ms_once / n_once
         del layers, lm_head
     except Exception as e:
         stack = {"error": str(e)}

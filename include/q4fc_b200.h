@@ -135,6 +135,28 @@ int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq
             int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
             q4fc_stream_t stream);
 
+/* ---- activations quantized once, used by several FCs ------------------------------------------------
+ * In the reference every FC quantizes its input itself, so the output of one normalization is quantized
+ * three times (q, k, v projections) or twice (gate, up) -- chatllama/main.py:344-368.  These entry points
+ * split the two steps.  xq is a device buffer of q4fc_xq_bytes(rows, K, group_k) bytes, 256-byte aligned:
+ * int8 codes [rows][Kg*group_k], then (256-byte aligned) fp32 [Kg][16] with entry 2m = scale of row m and
+ * entry 2m+1 = group sum of row m (Q4_1), or the bits of 8 * sum of codes with want_isum (Q4_0 with
+ * Q4FC_FLAG_NIBBLE_SIGNED).  rows <= 8.  Codes and scales are bit-equal to FC_dynamic_quantize_x
+ * (ops/op_fc.hpp:221-272); q4fc_fc_decode_q8 on them gives the bytes q4fc_fc_decode gives on the fp32 input.
+ *   q4fc_quant_x_q8      the quantizer alone.
+ *   q4fc_rmsnorm_quant   replaces llmops.rmsnorm (ops/op_misc.hpp:142-181) + that quantizer: normalizes each
+ *                        row (bit-equal to the reference: same eight running sums, same fold, IEEE division
+ *                        and square root) and quantizes it; y (fp32 [rows][ldy]) receives the normalized
+ *                        values unless NULL.  K % 8 == 0 as in the reference, x / weight / y 16-byte aligned.
+ *   q4fc_fc_decode_q8    the decode FC on such a buffer. */
+size_t q4fc_xq_bytes(int64_t rows, int64_t K, int group_k);
+int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int group_k, int want_isum, void* xq,
+                    unsigned flags, q4fc_stream_t stream);
+int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
+                       int64_t ldy, int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream);
+int q4fc_fc_decode_q8(const void* xq, int64_t rows, int64_t K, const void* wq, int64_t Ng, int64_t Kg, int qtype,
+                      int group_k, int64_t N, float* y, int64_t ldy, unsigned flags, q4fc_stream_t stream);
+
 /* No counterpart in the reference.  q4fc_fc_decode for callers that cannot
  * allocate device memory -- hosts that give all of it to their own arena at
  * start-up, or that run under a budget where a late cudaMalloc may fail or

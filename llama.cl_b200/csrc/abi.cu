@@ -246,6 +246,81 @@ int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const v
                                     y, ldy, flags, static_cast<cudaStream_t>(stream), ws, ws_bytes);
 }
 
+size_t q4fc_xq_bytes(int64_t rows, int64_t K, int group_k) {
+    if ((group_k != 32 && group_k != 128) || rows < 0 || K < 0) return 0;
+    return quant_pre_bytes(rows, K, group_k);
+}
+
+static int check_xq_args(const char* who, int64_t rows, int64_t K, int group_k, const void* xq) {
+    if (group_k != 32 && group_k != 128) {
+        set_error("%s: group_k=%d is neither 32 nor 128", who, group_k);
+        return Q4FC_EVARIANT;
+    }
+    if (rows < 0 || rows > kMaxDecodeRows || K <= 0) {
+        set_error("%s: rows=%lld must be 0..%d and K=%lld positive", who, (long long)rows, kMaxDecodeRows, (long long)K);
+        return rows > kMaxDecodeRows ? Q4FC_ELIMIT : Q4FC_EINVAL;
+    }
+    if (rows > 0 && (!xq || !aligned(xq, 256))) {
+        set_error("%s: xq is null or not 256-byte aligned", who);
+        return xq ? Q4FC_EALIGN : Q4FC_EINVAL;
+    }
+    return Q4FC_OK;
+}
+
+int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int group_k, int want_isum, void* xq,
+                    unsigned flags, q4fc_stream_t stream) {
+    if (int rc = check_xq_args("quant_x_q8", rows, K, group_k, xq)) return rc;
+    if (rows == 0) return Q4FC_OK;
+    if (!x || ldx < K || !aligned(x, 4)) {
+        set_error("quant_x_q8: null or misaligned x, or ldx < K");
+        return Q4FC_EINVAL;
+    }
+    const int64_t Kg = (K + group_k - 1) / group_k;
+    uint8_t* base = static_cast<uint8_t*>(xq);
+    return launch_quant_x_pre(x, (int)rows, K, ldx, group_k, want_isum != 0, reinterpret_cast<int8_t*>(base),
+                              reinterpret_cast<float*>(base + align_up((size_t)(rows * Kg * group_k), 256)),
+                              (flags & Q4FC_FLAG_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
+                       int64_t ldy, int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream) {
+    if (int rc = check_xq_args("rmsnorm_quant", rows, K, group_k, xq)) return rc;
+    if (rows == 0) return Q4FC_OK;
+    if (K % 8 != 0) {
+        set_error("rmsnorm_quant: K=%lld must be a multiple of 8 (as in the reference)", (long long)K);
+        return Q4FC_EINVAL;
+    }
+    if (!x || !weight || ldx < K || (y && ldy < K)) {
+        set_error("rmsnorm_quant: null pointer or leading dimension smaller than K");
+        return Q4FC_EINVAL;
+    }
+    if (!aligned(x, 16) || !aligned(weight, 16) || (y && !aligned(y, 16)) || ldx % 4 != 0 || (y && ldy % 4 != 0)) {
+        set_error("rmsnorm_quant: x, weight and y need 16-byte alignment and leading dimensions divisible by 4");
+        return Q4FC_EALIGN;
+    }
+    const int64_t Kg = (K + group_k - 1) / group_k;
+    uint8_t* base = static_cast<uint8_t*>(xq);
+    return launch_rmsnorm_quant(x, (int)rows, K, ldx, weight, eps, y, ldy, group_k, want_isum != 0,
+                                reinterpret_cast<int8_t*>(base),
+                                reinterpret_cast<float*>(base + align_up((size_t)(rows * Kg * group_k), 256)),
+                                (flags & Q4FC_FLAG_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_fc_decode_q8(const void* xq, int64_t rows, int64_t K, const void* wq, int64_t Ng, int64_t Kg, int qtype,
+                      int group_k, int64_t N, float* y, int64_t ldy, unsigned flags, q4fc_stream_t stream) {
+    if (int rc = check_xq_args("fc_decode_q8", rows, K, group_k, xq)) return rc;
+    // the codes stand in for x in the shared argument checks (pointer non-null, 4-byte aligned)
+    if (int rc = check_fc_args("fc_decode_q8", static_cast<const float*>(xq), rows, K, K, wq, Ng, Kg, qtype, group_k, N,
+                               y, ldy))
+        return rc;
+    if (flags & Q4FC_FLAG_STREAMK) {
+        set_error("fc_decode_q8: Q4FC_FLAG_STREAMK is not available for pre-quantized activations");
+        return Q4FC_EINVAL;
+    }
+    return launch_fc_decode_cluster(nullptr, (int)rows, K, K, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k,
+                                    N, y, ldy, flags, static_cast<cudaStream_t>(stream), nullptr, 0, xq);
+}
+
 int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
                     int qtype, int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
                     unsigned flags, q4fc_stream_t stream) {

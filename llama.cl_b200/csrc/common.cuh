@@ -63,7 +63,10 @@ int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uin
 // cluster form of the decode kernel (no global scratch)
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
-                             cudaStream_t s, void* ws = nullptr, size_t ws_bytes = 0);
+                             cudaStream_t s, void* ws = nullptr, size_t ws_bytes = 0, const void* xq = nullptr);
+// RMS normalization fused with the quantizer (rmsnorm_quant.cu); writes the pre-quantized format
+int launch_rmsnorm_quant(const float* x, int rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
+                         int64_t ldy, int G, bool want_isum, int8_t* codes, float* sc, bool pdl, cudaStream_t s);
 // quantizing launch in front of the decode FC for large rows x K (scratch layout: quant_x.cu)
 size_t quant_pre_bytes(int64_t rows, int64_t K, int G);
 int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, bool want_isum, int8_t* codes,

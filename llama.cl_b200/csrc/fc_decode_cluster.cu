@@ -38,9 +38,9 @@ int64_t pre_quant_min_values() {
 
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
-                             cudaStream_t s, void* ws, size_t ws_bytes) {
+                             cudaStream_t s, void* ws, size_t ws_bytes, const void* xq) {
     return launch_cluster_impl<false>(x, rows, K, ldx, wq, Ng, Kg, qtype, G, N, y, ldy, flags, s, nullptr, ws,
-                                      ws_bytes);
+                                      ws_bytes, xq);
 }
 
 }  // namespace q4fc

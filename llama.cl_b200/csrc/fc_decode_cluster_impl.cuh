@@ -627,7 +627,8 @@ constexpr int64_t kPreQuantMinValues = 40 * 1024;
 template <bool TP>
 int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
                         int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags, cudaStream_t s,
-                        const q4fc_tp_site* tp, void* ws = nullptr, size_t ws_bytes = 0) {
+                        const q4fc_tp_site* tp, void* ws = nullptr, size_t ws_bytes = 0,
+                        const void* xq_given = nullptr) {
     // a rank without columns still launches nothing: its peers count only the stripes that exist
     if (rows == 0 || N == 0) return Q4FC_OK;
     const DeviceInfo* di = device_info();
@@ -652,7 +653,13 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
     // pre-quantized input: scratch at its fixed place in the workspace, behind what the stream-K form uses
     bool preq = false;
     p.xq = nullptr, p.xsc = nullptr, p.xq_stride = Kg * G;
-    if (!TP && ws != nullptr && ((flags & Q4FC_FLAG_PREQUANT) || (int64_t)rows * K >= pre_quant_min_values()) &&
+    if (!TP && xq_given != nullptr) {
+        // the caller quantized the activations already (q4fc_quant_x_q8 / q4fc_rmsnorm_quant)
+        const uint8_t* base = static_cast<const uint8_t*>(xq_given);
+        p.xq = reinterpret_cast<const int8_t*>(base);
+        p.xsc = reinterpret_cast<const float*>(base + align_up((size_t)(rows * Kg * G), 256));
+        preq = true;
+    } else if (!TP && ws != nullptr && ((flags & Q4FC_FLAG_PREQUANT) || (int64_t)rows * K >= pre_quant_min_values()) &&
         (size_t)Ng * 4 <= kWsCounterCapacity && ws_bytes >= decode_prequant_offset() + quant_pre_bytes(rows, K, G)) {
         uint8_t* base = static_cast<uint8_t*>(ws) + decode_prequant_offset();
         p.xq = reinterpret_cast<const int8_t*>(base);
@@ -689,7 +696,7 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
                   di->max_smem_optin);
         return Q4FC_ELIMIT;
     }
-    if (preq) {
+    if (preq && xq_given == nullptr) {
         if (int rc = launch_quant_x_pre(x, rows, K, ldx, G, sgn, const_cast<int8_t*>(p.xq),
                                         const_cast<float*>(p.xsc), pdl, s))
             return rc;
@@ -697,7 +704,7 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
     // behind its own quantizing launch the FC always starts early: its weight loads run beside that launch
-    fill_launch_config(cfg, attr, p.nc * p.cs, p.cs, smem, pdl || preq, s);
+    fill_launch_config(cfg, attr, p.nc * p.cs, p.cs, smem, pdl || (preq && xq_given == nullptr), s);
     void* args[] = {const_cast<ClusterParams*>(&p)};
     Q4FC_CUDA_OK(cudaLaunchKernelExC(&cfg, v->fn, args));
     return Q4FC_OK;

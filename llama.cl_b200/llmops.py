@@ -180,6 +180,105 @@ def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_s
     return out
 
 
+class QuantizedActivations:
+    """Activations quantized once for several FCs (``q4fc_xq_*`` format): int8 codes ``[rows][Kg*G]`` followed
+    by ``[Kg][16]`` scales / group sums, in one device buffer.  Made by ``quantize_activations`` or
+    ``rmsnorm_quantize``, consumed by ``fc_Q4A_q8``."""
+
+    def __init__(self, B: int, M: int, K: int, group_k: int, signed: bool, device: torch.device) -> None:
+        self.B, self.M, self.K, self.group_k, self.signed = B, M, K, group_k, signed
+        self.rows = B * M
+        with torch.cuda.device(device):
+            nbytes = int(_cabi.lib().q4fc_xq_bytes(self.rows, K, group_k))
+        if nbytes == 0 and self.rows > 0:
+            raise RuntimeError(f"unsupported group_k={group_k}")
+        self.buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+
+    @property
+    def Kg(self) -> int:
+        return (self.K + self.group_k - 1) // self.group_k
+
+    def codes(self) -> torch.Tensor:
+        """int8 ``[rows, Kg*G]`` view of the codes."""
+        n = self.rows * self.Kg * self.group_k
+        return self.buf[:n].view(torch.int8).view(self.rows, self.Kg * self.group_k)
+
+    def scales_and_sums(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """fp32 ``[rows, Kg]`` scales and group sums (views into the ``[Kg][16]`` block)."""
+        off = (self.rows * self.Kg * self.group_k + 255) // 256 * 256
+        sc = self.buf[off: off + self.Kg * 64].view(torch.float32).view(self.Kg, 8, 2)
+        return sc[:, : self.rows, 0].t(), sc[:, : self.rows, 1].t()
+
+
+def _check_rows(rows: int) -> None:
+    if rows > 8:
+        raise RuntimeError(f"pre-quantized activations serve the decode kernel: B*M = {rows} exceeds 8")
+
+
+def quantize_activations(input: torch.Tensor, group_k: int, *, nibble_signed: bool = False, pdl: bool = False,
+                         out: QuantizedActivations | None = None) -> QuantizedActivations:
+    """FC_dynamic_quantize_x (ops/op_fc.hpp:221-272) once, for every FC that reads ``input`` ``[B, M, K]``."""
+    _require_cuda(input, "input", torch.float32, 3)
+    B, M, K = input.shape
+    _check_rows(B * M)
+    xq = out if out is not None else QuantizedActivations(B, M, K, group_k, nibble_signed, input.device)
+    with torch.cuda.device(input.device):
+        _cabi.check(_cabi.lib().q4fc_quant_x_q8(input.data_ptr(), B * M, K, K, group_k, int(nibble_signed),
+                                                xq.buf.data_ptr(), FLAG_PDL if pdl else 0,
+                                                _stream_ptr(input.device)), "quantize_activations")
+    return xq
+
+
+def rmsnorm_quantize(input: torch.Tensor, weight: torch.Tensor, eps: float, group_k: int, *,
+                     normalized: torch.Tensor | None = None, nibble_signed: bool = False, pdl: bool = False,
+                     out: QuantizedActivations | None = None) -> QuantizedActivations:
+    """``llmops.rmsnorm`` (ops/op_misc.hpp:142-181) and the quantizer of the FCs behind it in one kernel.
+
+    ``input`` fp32 ``[B, M, K]`` is left untouched (the reference normalizes a clone in place,
+    chatllama/main.py:345-346); ``normalized`` (same shape), when given, receives the normalized values, which
+    are bit-equal to the reference's."""
+    _require_cuda(input, "input", torch.float32, 3)
+    _require_cuda(weight, "weight", torch.float32, 1)
+    B, M, K = input.shape
+    _check_rows(B * M)
+    if weight.shape[0] != K:
+        raise RuntimeError(f"weight has {weight.shape[0]} elements, the rows {K}")
+    if normalized is not None:
+        _require_cuda(normalized, "normalized", torch.float32, 3)
+        if normalized.shape != input.shape:
+            raise RuntimeError("normalized: shape differs from input")
+    xq = out if out is not None else QuantizedActivations(B, M, K, group_k, nibble_signed, input.device)
+    with torch.cuda.device(input.device):
+        _cabi.check(_cabi.lib().q4fc_rmsnorm_quant(
+            input.data_ptr(), B * M, K, K, weight.data_ptr(), float(eps),
+            normalized.data_ptr() if normalized is not None else None, K, group_k, int(nibble_signed),
+            xq.buf.data_ptr(), FLAG_PDL if pdl else 0, _stream_ptr(input.device)), "rmsnorm_quantize")
+    return xq
+
+
+def fc_Q4A_q8(xq: QuantizedActivations, wei_quantized: torch.Tensor, N: int, *, out: torch.Tensor | None = None,
+              pdl: bool = False) -> torch.Tensor:
+    """``fc_Q4A`` on activations that were quantized beforehand: the same bytes as ``fc_Q4A(input, ...)``."""
+    _require_cuda(wei_quantized, "wei_quantized", torch.int8, 3)
+    Ng, Kg, bs = wei_quantized.shape
+    q, G = _cabi.infer_variant(bs)
+    if G != xq.group_k or Kg != xq.Kg:
+        raise RuntimeError(f"activations quantized for group {xq.group_k} x {xq.Kg}, weights are group {G} x {Kg}")
+    N = int(N)
+    if out is None:
+        out = torch.empty((xq.B, xq.M, N), dtype=torch.float32, device=wei_quantized.device)
+    else:
+        _require_cuda(out, "out", torch.float32, 3)
+        if tuple(out.shape) != (xq.B, xq.M, N):
+            raise RuntimeError(f"out: expected shape {(xq.B, xq.M, N)}, got {tuple(out.shape)}")
+    flags = (FLAG_PDL if pdl else 0) | (FLAG_NIBBLE_SIGNED if (xq.signed and q == Q4_0) else 0)
+    with torch.cuda.device(wei_quantized.device):
+        _cabi.check(_cabi.lib().q4fc_fc_decode_q8(xq.buf.data_ptr(), xq.rows, xq.K, wei_quantized.data_ptr(), Ng, Kg,
+                                                  q, G, N, out.data_ptr(), N, flags,
+                                                  _stream_ptr(wei_quantized.device)), "fc_Q4A_q8")
+    return out
+
+
 def fc_Q4A2(input, wei_quantized, N):
     """Bound by the reference (ops/main.cpp:161) but its body is compiled out (ops/op_fc.hpp:428-623)."""
     raise RuntimeError("fc_Q4A2 has no implementation in the reference; use fc_Q4A")

@@ -62,6 +62,7 @@ class _Restated:
             lib.oracle_dequant.argtypes = [u8p, i64, i64, i32, i32, i32, fp]
             lib.oracle_quant_x.argtypes = [fp, i64, i64, i32, f32, i8p, fp, fp]
             lib.oracle_fc.argtypes = [fp, i64, i64, u8p, i64, i64, i32, i32, i64, i32, fp, i64]
+            lib.oracle_rmsnorm.argtypes = [fp, i64, i64, fp, f32]
             lib.oracle_f32_to_f16.argtypes = [f32]
             lib.oracle_f32_to_f16.restype = C.c_uint16
             lib.oracle_f16_to_f32.argtypes = [C.c_uint16]
@@ -119,6 +120,16 @@ class _Restated:
                                 int(nibble_signed), _p(y, C.c_float), N)
         if rc:
             raise RuntimeError(f"oracle_fc failed ({rc})")
+        return y
+
+    def rmsnorm(self, x, weight, eps: float) -> np.ndarray:
+        """llmops.rmsnorm (ops/op_misc.hpp:142-181) on a copy of ``x`` [..., K]."""
+        y = _f32(x).copy()
+        w = _f32(weight)
+        K = y.shape[-1]
+        rc = self.lib.oracle_rmsnorm(_p(y, C.c_float), y.size // K, K, _p(w, C.c_float), eps)
+        if rc:
+            raise RuntimeError(f"oracle_rmsnorm failed ({rc})")
         return y
 
     def f16_bits(self, v: float) -> int:

@@ -333,6 +333,32 @@ int oracle_fc(const float* x, int64_t rows, int64_t K, const uint8_t* wq, int64_
     return 0;
 }
 
+/* ---- rmsnorm, op_misc.hpp:142-181, in place on x [rows][K] ------------------
+ * Eight running sums: lane j takes x[8i+j]^2 for i = 0, 1, ... with one fused
+ * multiply-add each (vfmadd); they are folded as ((s4+s0)+(s6+s2)) +
+ * ((s5+s1)+(s7+s3)) (_mm256_reduce_add_ps, utils.hpp:92-98).  rms = sum / K,
+ * r = 1 / sqrt(rms + eps), x = (x * r) * w with both products rounded. */
+int oracle_rmsnorm(float* x, int64_t rows, int64_t K, const float* w, float eps) {
+    if (K % 8 != 0) return 1; /* the reference asserts hidden_states % 8 == 0 */
+    for (int64_t m = 0; m < rows; m++) {
+        float* src = x + m * K;
+        float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int64_t i = 0; i < K; i += 8)
+            for (int j = 0; j < 8; j++) s[j] = fmaf(src[i + j], src[i + j], s[j]);
+        float a[4];
+        for (int j = 0; j < 4; j++) a[j] = s[4 + j] + s[j];
+        const float b0 = a[0] + a[2], b1 = a[1] + a[3];
+        const float sum = b0 + b1;
+        const float rms = sum / (float)K;
+        const float r = 1.0f / sqrtf(rms + eps);
+        for (int64_t i = 0; i < K; i++) {
+            float v = src[i] * r;
+            src[i] = v * w[i];
+        }
+    }
+    return 0;
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

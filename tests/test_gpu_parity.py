@@ -496,3 +496,67 @@ def test_host_fc_group(lib_built):
             assert torch.equal(y, pkg.llmops.fc_Q4A(x.to(dev), wq, N, path="decode").cpu())
     with pytest.raises(RuntimeError):
         group([torch.zeros(1, 1, 1024)])
+
+
+@pytest.mark.parametrize("qname,G,signed", [("q4_1", 128, False), ("q4_1", 32, False), ("q4_0", 32, True)])
+def test_quantize_once_then_several_fcs(lib_built, qname, G, signed):
+    """quantize_activations + fc_Q4A_q8: codes and scales bit-equal to the oracle's quantizer, FC outputs the
+    same bytes as fc_Q4A on the fp32 input, for several FCs sharing one quantized input."""
+    import llama_cl_b200 as pkg
+    from oracle import cpu
+
+    g = torch.Generator().manual_seed(31)
+    for rows, K in [(1, 4096), (8, 1024), (3, 1160)]:  # the last: ragged final group
+        x = torch.randn(1, rows, K, generator=g)
+        xq = pkg.llmops.quantize_activations(x.cuda(), G, nibble_signed=signed)
+        scale = 1.0 if qname == "q4_1" else 1 / 16
+        c0, s0, g0 = cpu.restated.quant_x(x.numpy(), G, 1.0)
+        assert np.array_equal(xq.codes().cpu().numpy(), c0.reshape(rows, -1))
+        sc, gs = xq.scales_and_sums()
+        assert np.array_equal(sc.cpu().numpy(), s0.reshape(rows, -1))
+        if not signed:
+            assert np.allclose(gs.cpu().numpy(), g0.reshape(rows, -1), rtol=1e-5, atol=1e-5)  # tree-ordered sums
+        for N in (96, 1000):
+            W = (torch.randn(N, K, generator=g) * 0.02).cuda()
+            wq = pkg.llmops.offline_FC_quant_Q4A(W, qtype=qname, group_k=G)
+            want = pkg.llmops.fc_Q4A(x.cuda(), wq, N, path="decode", nibble_signed=signed,
+                                     workspace=pkg.llmops.Workspace(4096, torch.device("cuda")))
+            got = pkg.llmops.fc_Q4A_q8(xq, wq, N)
+            assert torch.equal(got, want), (rows, K, N, scale)
+    with pytest.raises(RuntimeError):
+        pkg.llmops.quantize_activations(torch.zeros(1, 9, 256, device="cuda"), G)
+
+
+def test_rmsnorm_quantize_matches_the_reference_rows(lib_built):
+    """rmsnorm fused with the quantizer: normalized rows bit-equal to the reference's llmops.rmsnorm (fixture
+    from its compiled module), codes and scales bit-equal to quantizing those rows, and the FC behind it the
+    same bytes as the two-step path."""
+    import llama_cl_b200 as pkg
+    from oracle import cpu
+
+    f = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rmsnorm_ref.npz"))
+    g = torch.Generator().manual_seed(32)
+    for i in range(int(f["cases"])):
+        x, w, eps, y = f[f"x{i}"], f[f"w{i}"], float(f[f"eps{i}"]), f[f"y{i}"]
+        rows, K = x.shape[1], x.shape[2]
+        for G in (32, 128):
+            if K % G:
+                continue
+            xd = torch.from_numpy(x).cuda()
+            normalized = torch.empty_like(xd)
+            xq = pkg.llmops.rmsnorm_quantize(xd, torch.from_numpy(w).cuda(), eps, G, normalized=normalized)
+            assert torch.equal(xd.cpu(), torch.from_numpy(x))  # the input is left alone
+            assert np.array_equal(normalized.cpu().numpy(), y), (i, G)
+            c0, s0, _ = cpu.restated.quant_x(y, G, 1.0)
+            assert np.array_equal(xq.codes().cpu().numpy(), c0.reshape(rows, -1))
+            assert np.array_equal(xq.scales_and_sums()[0].cpu().numpy(), s0.reshape(rows, -1))
+            # without the normalized output the quantized result is the same
+            xq2 = pkg.llmops.rmsnorm_quantize(xd, torch.from_numpy(w).cuda(), eps, G)
+            assert torch.equal(xq2.buf, xq.buf)
+            W = (torch.randn(160, K, generator=g) * 0.02).cuda()
+            wq = pkg.llmops.offline_FC_quant_Q4A(W, qtype="q4_1", group_k=G)
+            want = pkg.llmops.fc_Q4A(torch.from_numpy(y).cuda(), wq, 160, path="decode",
+                                     workspace=pkg.llmops.Workspace(4096, torch.device("cuda")))
+            assert torch.equal(pkg.llmops.fc_Q4A_q8(xq, wq, 160), want)
+    with pytest.raises(RuntimeError):
+        pkg.llmops.rmsnorm_quantize(torch.zeros(1, 1, 12, device="cuda"), torch.ones(12, device="cuda"), 1e-5, 32)

@@ -134,3 +134,17 @@ def test_empty_inputs(oracle):
     assert oracle.restated.pack(np.zeros((0, 64), np.float32), 1, 32).shape == (0, 2, 640)
     c, s, gs = oracle.restated.quant_x(np.zeros((0, 64), np.float32), 32)
     assert c.shape == (0, 64) and s.shape == (0, 2)
+
+
+def test_rmsnorm_restatement_matches_the_reference_rows():
+    """Rows returned by the reference's own llmops.rmsnorm (fixture from its compiled module): bit-equal."""
+    import numpy as np
+
+    from oracle import cpu
+
+    f = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rmsnorm_ref.npz"))
+    for i in range(int(f["cases"])):
+        got = cpu.restated.rmsnorm(f[f"x{i}"], f[f"w{i}"], float(f[f"eps{i}"]))
+        assert np.array_equal(got, f[f"y{i}"]), i
+    with pytest.raises(RuntimeError):
+        cpu.restated.rmsnorm(np.zeros((1, 1, 12), np.float32), np.ones(12, np.float32), 1e-5)  # K % 8 != 0
