@@ -148,12 +148,19 @@ int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq
  *                        row (bit-equal to the reference: same eight running sums, same fold, IEEE division
  *                        and square root) and quantizes it; y (fp32 [rows][ldy]) receives the normalized
  *                        values unless NULL.  K % 8 == 0 as in the reference, x / weight / y 16-byte aligned.
+ *   q4fc_add_rmsnorm_quant  the same with the residual addition in front of it (llmops.iadd,
+ *                        chatllama/main.py:359): the row that is normalized is x + residual, and sum_out
+ *                        (may be NULL, may alias x or residual) receives that sum -- the new residual
+ *                        stream.  residual and sum_out share x's row stride ldx.
  *   q4fc_fc_decode_q8    the decode FC on such a buffer. */
 size_t q4fc_xq_bytes(int64_t rows, int64_t K, int group_k);
 int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int group_k, int want_isum, void* xq,
                     unsigned flags, q4fc_stream_t stream);
 int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
                        int64_t ldy, int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream);
+int q4fc_add_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int64_t rows, int64_t K, int64_t ldx,
+                           const float* weight, float eps, float* y, int64_t ldy, int group_k, int want_isum,
+                           void* xq, unsigned flags, q4fc_stream_t stream);
 int q4fc_fc_decode_q8(const void* xq, int64_t rows, int64_t K, const void* wq, int64_t Ng, int64_t Kg, int qtype,
                       int group_k, int64_t N, float* y, int64_t ldy, unsigned flags, q4fc_stream_t stream);
 

@@ -284,7 +284,22 @@ int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int gr
 
 int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
                        int64_t ldy, int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream) {
+    return q4fc_add_rmsnorm_quant(x, nullptr, nullptr, rows, K, ldx, weight, eps, y, ldy, group_k, want_isum, xq,
+                                  flags, stream);
+}
+
+int q4fc_add_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int64_t rows, int64_t K, int64_t ldx,
+                           const float* weight, float eps, float* y, int64_t ldy, int group_k, int want_isum,
+                           void* xq, unsigned flags, q4fc_stream_t stream) {
     if (int rc = check_xq_args("rmsnorm_quant", rows, K, group_k, xq)) return rc;
+    if (sum_out && !residual) {
+        set_error("rmsnorm_quant: sum_out without residual");
+        return Q4FC_EINVAL;
+    }
+    if ((residual && !aligned(residual, 16)) || (sum_out && !aligned(sum_out, 16))) {
+        set_error("rmsnorm_quant: residual and sum_out need 16-byte alignment");
+        return Q4FC_EALIGN;
+    }
     if (rows == 0) return Q4FC_OK;
     if (K % 8 != 0) {
         set_error("rmsnorm_quant: K=%lld must be a multiple of 8 (as in the reference)", (long long)K);
@@ -300,7 +315,7 @@ int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, con
     }
     const int64_t Kg = (K + group_k - 1) / group_k;
     uint8_t* base = static_cast<uint8_t*>(xq);
-    return launch_rmsnorm_quant(x, (int)rows, K, ldx, weight, eps, y, ldy, group_k, want_isum != 0,
+    return launch_rmsnorm_quant(x, residual, sum_out, (int)rows, K, ldx, weight, eps, y, ldy, group_k, want_isum != 0,
                                 reinterpret_cast<int8_t*>(base),
                                 reinterpret_cast<float*>(base + align_up((size_t)(rows * Kg * group_k), 256)),
                                 (flags & Q4FC_FLAG_PDL) != 0, static_cast<cudaStream_t>(stream));

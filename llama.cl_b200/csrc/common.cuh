@@ -65,7 +65,8 @@ int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, c
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
                              cudaStream_t s, void* ws = nullptr, size_t ws_bytes = 0, const void* xq = nullptr);
 // RMS normalization fused with the quantizer (rmsnorm_quant.cu); writes the pre-quantized format
-int launch_rmsnorm_quant(const float* x, int rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
+int launch_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int rows, int64_t K, int64_t ldx,
+                         const float* weight, float eps, float* y,
                          int64_t ldy, int G, bool want_isum, int8_t* codes, float* sc, bool pdl, cudaStream_t s);
 // quantizing launch in front of the decode FC for large rows x K (scratch layout: quant_x.cu)
 size_t quant_pre_bytes(int64_t rows, int64_t K, int G);

@@ -18,6 +18,10 @@
 // reference's FCs would compute from its own rmsnorm output; the group sums are tree-ordered like the decode
 // kernel's.
 //
+// Optionally the residual addition in front of the normalization (llmops.iadd, chatllama/main.py:359) is done
+// on the way in: the row that is normalized is x + residual (one IEEE add per element, as the reference's), and
+// the sum can be written out as the new residual stream.
+//
 // One CTA per row: the row is first copied to shared memory by all warps, eight lanes run the chains, then
 // every warp quantizes 128-k chunks (one 512-byte read of shared memory each).
 #include "common.cuh"
@@ -30,7 +34,9 @@ constexpr int kRnThreads = 256;
 __device__ __forceinline__ int sat8(int v) { return min(127, max(-128, v)); }
 
 template <int G>
-__global__ void __launch_bounds__(kRnThreads) rmsnorm_quant_kernel(const float* __restrict__ x, int64_t K, int64_t ldx,
+__global__ void __launch_bounds__(kRnThreads) rmsnorm_quant_kernel(const float* x, const float* residual,
+                                                                   float* sum_out /* may alias x or residual */,
+                                                                   int64_t K, int64_t ldx,
                                                                    const float* __restrict__ weight, float eps,
                                                                    float* __restrict__ y, int64_t ldy, int64_t Kg,
                                                                    int want_isum, int8_t* __restrict__ codes,
@@ -44,8 +50,16 @@ __global__ void __launch_bounds__(kRnThreads) rmsnorm_quant_kernel(const float* 
     pdl_launch_dependents();
     pdl_wait_prior_grid();  // the activations may come from the kernel before
 
-    for (int64_t i = threadIdx.x * 4; i < K; i += kRnThreads * 4)  // K % 8 == 0 (checked by the launcher)
-        *reinterpret_cast<float4*>(row + i) = __ldcg(reinterpret_cast<const float4*>(src + i));
+    for (int64_t i = threadIdx.x * 4; i < K; i += kRnThreads * 4) {  // K % 8 == 0 (checked by the launcher)
+        float4 a = __ldcg(reinterpret_cast<const float4*>(src + i));
+        if (residual != nullptr) {
+            // the reference's iadd in front of the normalization (ops/op_misc.hpp:55-79): one IEEE add each
+            const float4 b = __ldcg(reinterpret_cast<const float4*>(residual + m * ldx + i));
+            a.x = __fadd_rn(a.x, b.x), a.y = __fadd_rn(a.y, b.y), a.z = __fadd_rn(a.z, b.z), a.w = __fadd_rn(a.w, b.w);
+            if (sum_out != nullptr) *reinterpret_cast<float4*>(sum_out + m * ldx + i) = a;
+        }
+        *reinterpret_cast<float4*>(row + i) = a;
+    }
     __syncthreads();
 
     if (warp == 0) {
@@ -131,7 +145,8 @@ __global__ void __launch_bounds__(kRnThreads) rmsnorm_quant_kernel(const float* 
 
 }  // namespace
 
-int launch_rmsnorm_quant(const float* x, int rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
+int launch_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int rows, int64_t K, int64_t ldx,
+                         const float* weight, float eps, float* y,
                          int64_t ldy, int G, bool want_isum, int8_t* codes, float* sc, bool pdl, cudaStream_t s) {
     if (rows == 0) return Q4FC_OK;
     const DeviceInfo* di = device_info();
@@ -163,7 +178,8 @@ int launch_rmsnorm_quant(const float* x, int rows, int64_t K, int64_t ldx, const
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     int wi = want_isum ? 1 : 0;
-    void* args[] = {&x, &K, &ldx, &weight, &eps, &y, &ldy, const_cast<int64_t*>(&Kg), &wi, &codes, &sc};
+    void* args[] = {&x,   &residual, &sum_out, &K,  &ldx,   &weight, &eps,
+                    &y,   &ldy,      const_cast<int64_t*>(&Kg), &wi, &codes, &sc};
     Q4FC_CUDA_OK(cudaLaunchKernelExC(&cfg, fn, args));
     return Q4FC_OK;
 }

@@ -230,13 +230,16 @@ def quantize_activations(input: torch.Tensor, group_k: int, *, nibble_signed: bo
 
 
 def rmsnorm_quantize(input: torch.Tensor, weight: torch.Tensor, eps: float, group_k: int, *,
-                     normalized: torch.Tensor | None = None, nibble_signed: bool = False, pdl: bool = False,
+                     normalized: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                     sum_out: torch.Tensor | None = None, nibble_signed: bool = False, pdl: bool = False,
                      out: QuantizedActivations | None = None) -> QuantizedActivations:
     """``llmops.rmsnorm`` (ops/op_misc.hpp:142-181) and the quantizer of the FCs behind it in one kernel.
 
     ``input`` fp32 ``[B, M, K]`` is left untouched (the reference normalizes a clone in place,
     chatllama/main.py:345-346); ``normalized`` (same shape), when given, receives the normalized values, which
-    are bit-equal to the reference's."""
+    are bit-equal to the reference's.  With ``residual`` the row that is normalized is ``input + residual``
+    (the reference's ``llmops.iadd`` in front of the norm, chatllama/main.py:359) and ``sum_out`` (may be
+    ``input`` or ``residual`` itself) receives that sum."""
     _require_cuda(input, "input", torch.float32, 3)
     _require_cuda(weight, "weight", torch.float32, 1)
     B, M, K = input.shape
@@ -247,10 +250,18 @@ def rmsnorm_quantize(input: torch.Tensor, weight: torch.Tensor, eps: float, grou
         _require_cuda(normalized, "normalized", torch.float32, 3)
         if normalized.shape != input.shape:
             raise RuntimeError("normalized: shape differs from input")
+    for name, t in (("residual", residual), ("sum_out", sum_out)):
+        if t is not None:
+            _require_cuda(t, name, torch.float32, 3)
+            if t.shape != input.shape:
+                raise RuntimeError(f"{name}: shape differs from input")
+    if sum_out is not None and residual is None:
+        raise RuntimeError("sum_out without residual")
     xq = out if out is not None else QuantizedActivations(B, M, K, group_k, nibble_signed, input.device)
     with torch.cuda.device(input.device):
-        _cabi.check(_cabi.lib().q4fc_rmsnorm_quant(
-            input.data_ptr(), B * M, K, K, weight.data_ptr(), float(eps),
+        _cabi.check(_cabi.lib().q4fc_add_rmsnorm_quant(
+            input.data_ptr(), residual.data_ptr() if residual is not None else None,
+            sum_out.data_ptr() if sum_out is not None else None, B * M, K, K, weight.data_ptr(), float(eps),
             normalized.data_ptr() if normalized is not None else None, K, group_k, int(nibble_signed),
             xq.buf.data_ptr(), FLAG_PDL if pdl else 0, _stream_ptr(input.device)), "rmsnorm_quantize")
     return xq

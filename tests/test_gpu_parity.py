@@ -558,5 +558,19 @@ def test_rmsnorm_quantize_matches_the_reference_rows(lib_built):
             want = pkg.llmops.fc_Q4A(torch.from_numpy(y).cuda(), wq, 160, path="decode",
                                      workspace=pkg.llmops.Workspace(4096, torch.device("cuda")))
             assert torch.equal(pkg.llmops.fc_Q4A_q8(xq, wq, 160), want)
+    # residual addition in front of the norm (llmops.iadd + clone + rmsnorm in the reference's layer)
+    x, w, eps = f["x1"], f["w1"], float(f["eps1"])
+    res = torch.randn(x.shape, generator=g).numpy()
+    summed = (x + res).astype(np.float32)
+    want_rows = cpu.restated.rmsnorm(summed, w, eps)
+    xd, rd = torch.from_numpy(x).cuda(), torch.from_numpy(res).cuda()
+    normalized, sum_out = torch.empty_like(xd), torch.empty_like(xd)
+    xq = pkg.llmops.rmsnorm_quantize(xd, torch.from_numpy(w).cuda(), eps, 128, residual=rd, sum_out=sum_out,
+                                     normalized=normalized)
+    assert np.array_equal(sum_out.cpu().numpy(), summed) and np.array_equal(normalized.cpu().numpy(), want_rows)
+    c0, _, _ = cpu.restated.quant_x(want_rows, 128, 1.0)
+    assert np.array_equal(xq.codes().cpu().numpy(), c0.reshape(x.shape[1], -1))
+    pkg.llmops.rmsnorm_quantize(xd, torch.from_numpy(w).cuda(), eps, 128, residual=rd, sum_out=rd)  # in place
+    assert np.array_equal(rd.cpu().numpy(), summed)
     with pytest.raises(RuntimeError):
         pkg.llmops.rmsnorm_quantize(torch.zeros(1, 1, 12, device="cuda"), torch.ones(12, device="cuda"), 1e-5, 32)
