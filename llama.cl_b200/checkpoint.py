@@ -27,20 +27,28 @@ _TENSOR_MODULE, _TENSOR_NAME = "llmops", "tensor"
 _OP_MODULES = ("__main__", "main")  # where the reference's op classes are found in a pickle
 
 
+def _canonical(array) -> np.ndarray:
+    """Contiguous, and carrying numpy's own dtype object for its type.  A dtype that comes out of a pickle is a
+    separate object; the pickler shares objects by identity, so a model in which loaded and freshly made arrays
+    mix would otherwise be written with the dtype spelled out more than once -- not as the reference writes it."""
+    a = np.ascontiguousarray(array)
+    return a.view(np.dtype(a.dtype.str))
+
+
 class HostTensor:
     """Stand-in for ``llmops.tensor`` on the host: holds the numpy array the reference pickled."""
 
     __slots__ = ("array",)
 
     def __init__(self, array) -> None:
-        self.array = np.ascontiguousarray(array)
+        self.array = _canonical(array)
 
     # the pickle protocol of ops/main.cpp:129-136: state = (numpy array,)
     def __getstate__(self):
         return (self.array,)
 
     def __setstate__(self, state) -> None:
-        self.array = state[0]
+        self.array = _canonical(state[0])
 
     @property
     def shape(self):
