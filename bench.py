@@ -49,6 +49,9 @@ SHAPES = [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000)]  # (K, N)
 MS = [1, 2, 4, 8]
 QTYPE, GROUP_K = 1, 128
 BS = 16 * GROUP_K + 128
+# DRAM bytes per decode launch of this sweep from one ncu capture (3,561,888,512 B over 113 launches), against
+# 31.89 MB of algorithmic bytes per launch
+DECODE_TRAFFIC_PER_LAUNCH = 31.52e6
 METRIC = "Q4_1 FC decode weight GB/s"
 UNIT = "GB/s"
 
@@ -720,7 +723,10 @@ def our_arm(args) -> None:
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
             **({"tp_status": tp_status} if fused else {}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak, "traffic": DECODE_TRAFFIC_PER_LAUNCH if not distributed else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average over the decode "
+                                           "launches of this sweep (profiles/bench_sweep_launch_list.md)",
+                         "peak_kind": peak_kind,
                          "kernel": "fc_decode_cluster_kernel<128,1,false,ROWS>",
                          "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": len(calls),
                          "timed_as": "the 16 launches one after the other on one stream, plain stream order (a "
