@@ -725,7 +725,7 @@ def our_arm(args) -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": DECODE_TRAFFIC_PER_LAUNCH if not distributed else None,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average over the decode "
-                                           "launches of this sweep (profiles/bench_sweep_launch_list.md)",
+                                           "launches of this sweep (launch-list summary under profiles/)",
                          "peak_kind": peak_kind,
                          "kernel": "fc_decode_cluster_kernel<128,1,false,ROWS>",
                          "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": len(calls),
