@@ -256,9 +256,9 @@ def our_arm(args) -> None:
     # and each call of the host-buffer leg stands alone
     sweep_sched = tp.TPSchedule(arena) if fused else None
 
-    def make_layer(sched, wq_, N_, max_rows=8):
+    def make_layer(sched, wq_, N_, max_rows=8, prequant=False):
         if fused:
-            return tp.FusedTPLinearQ4(sched, wq_, N_, max_rows=max_rows, pdl=True)
+            return tp.FusedTPLinearQ4(sched, wq_, N_, max_rows=max_rows, pdl=True, prequant=prequant)
         return tp.TPLinearQ4(wq_, N_, pdl=True, workspace=ws, path="decode")
 
     # ---- inputs: one packed weight per (shape, M); with TP each rank packs only its rows
@@ -273,7 +273,7 @@ def our_arm(args) -> None:
             wq = pkg.llmops.offline_FC_quant_Q4A(W[n0:n1].contiguous(), qtype="q4_1", group_k=GROUP_K)
             del W
             x = torch.randn((1, M, K), generator=gen, device=dev, dtype=torch.float32)
-            layer = make_layer(sweep_sched, wq, N) if distributed else None
+            layer = make_layer(sweep_sched, wq, N, prequant=args.lanes > 1) if distributed else None
             calls.append({"x": x, "wq": wq, "N": N, "n_local": n1 - n0, "M": M, "K": K, "layer": layer,
                           "y_full": torch.empty((1, M, N), device=dev, dtype=torch.float32) if fused else None,
                           "y": torch.empty((1, M, n1 - n0), device=dev, dtype=torch.float32)})
@@ -413,7 +413,7 @@ def our_arm(args) -> None:
         hosts = []
         for c in calls:
             if fused:
-                hosts.append(tp.HostFusedFC(arena, c["wq"], c["N"], max_rows=8, pdl=True,
+                hosts.append(tp.HostFusedFC(arena, c["wq"], c["N"], max_rows=8, pdl=True, prequant=n_lanes > 1,
                                             stream=lane_streams[len(hosts) % n_lanes]))
             elif distributed:
                 hosts.append(None)
@@ -681,7 +681,7 @@ def our_arm(args) -> None:
     # this library's kernels per timed step: the FC kernel of every call, plus -- side by side on one GPU --
     # the quantizing launch in front of each, or -- N-split -- the step barrier and one unpacking kernel per call
     if fused:
-        launches_per_step = 2 * len(calls) + 1
+        launches_per_step = (3 if n_lanes > 1 else 2) * len(calls) + 1
     elif distributed:
         launches_per_step = len(calls)
     elif n_lanes > 1:

@@ -214,6 +214,10 @@ typedef struct q4fc_tp_site {
     unsigned long long* y_peer[8];   /* every rank's stamped output [rows, ldy], own rank included */
     const unsigned long long* epoch; /* local step counter, advanced by q4fc_tp_step_begin */
     int* status;                     /* local int, set non-zero when a bounded wait ran out */
+    void* xq_scratch;                /* NULL, or q4fc_xq_bytes(rows, K, group_k) bytes of local scratch (256-byte
+                                        aligned): with a plain fp32 x the activations are then quantized once in a
+                                        small launch in front of the FC kernel (as Q4FC_FLAG_PREQUANT does for
+                                        q4fc_fc_decode) instead of by every cluster; ignored with x_stamped */
 } q4fc_tp_site;
 
 /* sizeof(q4fc_tp_site) as the library was built: bindings that mirror the struct check theirs against it */

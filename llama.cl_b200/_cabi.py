@@ -37,6 +37,7 @@ class TpSite(C.Structure):
         ("y_peer", C.c_void_p * 8),
         ("epoch", C.c_void_p),
         ("status", C.c_void_p),
+        ("xq_scratch", C.c_void_p),
     ]
 
 _lib = None

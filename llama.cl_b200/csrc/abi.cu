@@ -444,6 +444,10 @@ int q4fc_fc_decode_tp(const void* x, int64_t rows, int64_t K, int64_t ldx, const
             set_error("fc_decode_tp: y_peer[%d] is null or not 8-byte aligned", i);
             return Q4FC_EINVAL;
         }
+    if (site->xq_scratch && !aligned(site->xq_scratch, 256)) {
+        set_error("fc_decode_tp: xq_scratch needs 256-byte alignment");
+        return Q4FC_EALIGN;
+    }
     if (site->x_stamped && !aligned(x, 8)) {
         set_error("fc_decode_tp: a stamped x needs 8-byte alignment");
         return Q4FC_EALIGN;

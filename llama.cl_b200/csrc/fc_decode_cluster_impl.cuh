@@ -543,13 +543,10 @@ Variant* variant_of() {
     return &v;
 }
 
-// The pre-quantized form has one instantiation per block type (its row loops run to 8 with a run-time
-// bound); the multi-GPU form always quantizes in the kernel
+// The pre-quantized form has one instantiation per block type (its row loops run to 8 with a run-time bound)
 template <int G, int QTYPE, bool SIGNED, bool TP>
 Variant* variant_for_rows(int rows, bool preq) {
-    if constexpr (!TP) {
-        if (preq) return variant_of<G, QTYPE, SIGNED, 8, TP, true>();
-    }
+    if (preq) return variant_of<G, QTYPE, SIGNED, 8, TP, true>();
     if (rows <= 1) return variant_of<G, QTYPE, SIGNED, 1, TP, false>();
     if (rows <= 2) return variant_of<G, QTYPE, SIGNED, 2, TP, false>();
     if (rows <= 4) return variant_of<G, QTYPE, SIGNED, 4, TP, false>();
@@ -653,7 +650,13 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
     // pre-quantized input: scratch at its fixed place in the workspace, behind what the stream-K form uses
     bool preq = false;
     p.xq = nullptr, p.xsc = nullptr, p.xq_stride = Kg * G;
-    if (!TP && xq_given != nullptr) {
+    if (TP && tp->xq_scratch != nullptr && !tp->x_stamped) {
+        // multi-GPU form with a plain input: quantize once into the caller's scratch, in front of the FC kernel
+        uint8_t* base = static_cast<uint8_t*>(tp->xq_scratch);
+        p.xq = reinterpret_cast<const int8_t*>(base);
+        p.xsc = reinterpret_cast<const float*>(base + align_up((size_t)(rows * Kg * G), 256));
+        preq = true;
+    } else if (!TP && xq_given != nullptr) {
         // the caller quantized the activations already (q4fc_quant_x_q8 / q4fc_rmsnorm_quant)
         const uint8_t* base = static_cast<const uint8_t*>(xq_given);
         p.xq = reinterpret_cast<const int8_t*>(base);

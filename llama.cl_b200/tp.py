@@ -279,7 +279,7 @@ class FusedTPLinearQ4:
     kernel)."""
 
     def __init__(self, schedule: TPSchedule, wq_shard: torch.Tensor, N: int, *, max_rows: int = 8,
-                 pdl: bool = False, nibble_signed: bool = False) -> None:
+                 pdl: bool = False, nibble_signed: bool = False, prequant: bool = False) -> None:
         arena = schedule.arena
         self.schedule = schedule
         self.arena = arena
@@ -297,6 +297,14 @@ class FusedTPLinearQ4:
         self.ldy = self.Ng * 32
         self.y_off = arena.alloc(self.max_rows * self.ldy * 8)
         self.flags = (_cabi.FLAG_PDL if pdl else 0) | (_cabi.FLAG_NIBBLE_SIGNED if nibble_signed else 0)
+        # with a plain fp32 input: quantize it once in a small launch in front of the kernel (less repeated work
+        # when several FCs run side by side); inputs that are another layer's output are quantized in the kernel
+        self._xq = None
+        if prequant:
+            K = self.Kg * self.group_k
+            with torch.cuda.device(arena.device):
+                nbytes = int(_cabi.lib().q4fc_xq_bytes(self.max_rows, K, self.group_k))
+            self._xq = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=arena.device)
         self._sites: dict = {}
 
     def _site(self, stamped: bool) -> "_cabi.TpSite":
@@ -310,6 +318,7 @@ class FusedTPLinearQ4:
                 s.y_peer[r] = a.bases[r] + self.y_off
             s.epoch = a.local + self.schedule.epoch_off
             s.status = a.local + a.STATUS
+            s.xq_scratch = self._xq.data_ptr() if (self._xq is not None and not stamped) else None
             self._sites[stamped] = s
         return self._sites[stamped]
 

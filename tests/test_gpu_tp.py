@@ -158,6 +158,18 @@ def _fused_worker(rank, world, initfile, result_q):
             torch.cuda.synchronize()
             want = pkg.llmops.fc_Q4A(xg, full["q"], H)
             expect(torch.allclose(y, want, rtol=1e-3, atol=1e-4), f"solo schedule step {step}")
+        # a layer that quantizes its plain input once in front of the kernel: the same bytes as one that does not
+        sq = tp.TPSchedule(arena)
+        la = tp.FusedTPLinearQ4(sq, tp.shard_packed(full["up"], world, rank), I, pdl=True)
+        lb = tp.FusedTPLinearQ4(sq, tp.shard_packed(full["up"], world, rank), I, pdl=True, prequant=True)
+        for M in (1, 8):
+            g = torch.Generator().manual_seed(500 + M)
+            xm = torch.randn(1, M, H, generator=g).to(dev)
+            sq.step_begin()
+            ya, yb = la(xm).tensor(), lb(xm).tensor()
+            torch.cuda.synchronize()
+            expect(torch.equal(ya, yb), f"prequant layer M={M}")
+
         # host buffers in and out over the N-split FC, as a replayed graph, two row counts, fresh inputs
         hf = tp.HostFusedFC(arena, tp.shard_packed(full["up"], world, rank), I, max_rows=4, pdl=True)
         for step in range(3):
