@@ -25,9 +25,9 @@
 // before the programmatic-dependent-launch wait, because weights never depend
 // on the preceding kernel.
 //
-// A run longer than the two register steps is also requested into L2 with
-// cp.async.bulk.prefetch before the wait, so HBM keeps streaming while the
-// preceding kernel drains.
+// The two steps that follow the register steps are also requested into L2 with
+// cp.async.bulk.prefetch before the wait; more than that evicts lines of the
+// kernels running beside this one before they are used.
 //
 // Activations.  A warp reads 128 consecutive k of a row of the CTA's slice
 // (one 128-bit load per lane, a few in flight) and quantizes them in
@@ -70,6 +70,7 @@ namespace {
 constexpr int kCW = 4;  // warps per CTA
 constexpr int kCThreads = kCW * 32;
 constexpr int kMaxStripes = 16;  // stripes per cluster (bounds the shared-memory inbox)
+constexpr int kPrefetchSteps = 2;  // steps beyond the two in registers that a warp requests into L2 at its start
 constexpr uint32_t kNibMask = 0x0F0F0F0Fu;
 
 struct ClusterParams {
@@ -232,13 +233,16 @@ __global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const C
     load_step(cur);
     load_step(nxt);
     Q4FC_MARK(10);
-    // the rest of the run is requested into L2 after the register steps: issued ahead of them (tried) it
-    // delays the cluster-barrier arrival and the first loads, 7 % on the whole sweep
-    if (f1 - f0 > 2 * NBLK) {
+    // the next steps of the run are requested into L2 behind the register steps.  Measured: requesting the
+    // whole run (the first form) costs 6 % on the sweep and on the token pass -- kernels that run side by side
+    // then evict one another's lines before they are used; a window that rolls along with the loop is no
+    // better than none; issuing the requests ahead of the register steps delays those by 7 %.
+    const int f1p = min(f1, f0 + (2 + kPrefetchSteps) * NBLK);
+    if (f1p - f0 > 2 * NBLK) {
         const int pf = f0 + 2 * NBLK;
-        const int i_first = pf / Kc, i_last = (f1 - 1) / Kc;
+        const int i_first = pf / Kc, i_last = (f1p - 1) / Kc;
         for (int i = i_first + lane; i <= i_last; i += 32) {  // one contiguous piece per stripe
-            const int fb = max(pf, i * Kc), fe = min(f1, (i + 1) * Kc);
+            const int fb = max(pf, i * Kc), fe = min(f1p, (i + 1) * Kc);
             const uint8_t* a = p.wq + ((int64_t)(s0 + i) * p.Kg + k0 + (fb - i * Kc)) * BS;
             for (int done = 0; done < fe - fb; done += 16)
                 l2_prefetch(a + (int64_t)done * BS, (uint32_t)(min(16, fe - fb - done) * BS));
