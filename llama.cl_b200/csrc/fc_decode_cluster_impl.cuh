@@ -677,6 +677,10 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
     int dev = 0;
     Q4FC_CUDA_OK(cudaGetDevice(&dev));
     p.cs = 8;
+    // Clusters of 8 spread the in-kernel quantization over more CTAs and give the shortest single call; when
+    // the caller asks for the separate quantizing launch because calls run side by side, that reason is gone and
+    // clusters of 4 (cheaper barriers, finer placement) are 4 % faster on the whole (and 13 % slower alone).
+    if (preq && xq_given == nullptr && (TP || (flags & Q4FC_FLAG_PREQUANT))) p.cs = 4;
     while (p.cs > 1 && p.cs > Kg) p.cs /= 2;
     p.log2cs = 0;
     while ((1 << p.log2cs) < p.cs) p.log2cs++;
