@@ -69,8 +69,9 @@ enum {
     /* q4fc_fc_decode with a workspace: always quantize the activations in a small launch of their own in
      * front of the FC kernel (by default only for large rows x K).  The FC kernel otherwise quantizes
      * them itself, every cluster its own copy: the shortest path for one call at a time, but repeated
-     * work that competes for the SMs when several FCs run side by side on different streams.  Same
-     * results bit for bit. */
+     * work that competes for the SMs when several FCs run side by side on different streams.  Codes and
+     * scales are the same bit for bit; the kernel then also splits K over clusters of 4 instead of 8, so
+     * outputs agree within the rounding of the fp32 sums. */
     Q4FC_FLAG_PREQUANT = 8u
 };
 

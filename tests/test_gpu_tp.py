@@ -158,7 +158,8 @@ def _fused_worker(rank, world, initfile, result_q):
             torch.cuda.synchronize()
             want = pkg.llmops.fc_Q4A(xg, full["q"], H)
             expect(torch.allclose(y, want, rtol=1e-3, atol=1e-4), f"solo schedule step {step}")
-        # a layer that quantizes its plain input once in front of the kernel: the same bytes as one that does not
+        # a layer that quantizes its plain input once in front of the kernel: same codes and scales; its kernel
+        # splits K over clusters of 4 instead of 8, so the fp32 sums differ in the last bits only
         sq = tp.TPSchedule(arena)
         la = tp.FusedTPLinearQ4(sq, tp.shard_packed(full["up"], world, rank), I, pdl=True)
         lb = tp.FusedTPLinearQ4(sq, tp.shard_packed(full["up"], world, rank), I, pdl=True, prequant=True)
@@ -168,7 +169,7 @@ def _fused_worker(rank, world, initfile, result_q):
             sq.step_begin()
             ya, yb = la(xm).tensor(), lb(xm).tensor()
             torch.cuda.synchronize()
-            expect(torch.equal(ya, yb), f"prequant layer M={M}")
+            expect(torch.allclose(ya, yb, rtol=1e-4, atol=1e-5), f"prequant layer M={M}")
 
         # host buffers in and out over the N-split FC, as a replayed graph, two row counts, fresh inputs
         hf = tp.HostFusedFC(arena, tp.shard_packed(full["up"], world, rank), I, max_rows=4, pdl=True)
