@@ -49,7 +49,7 @@ SHAPES = [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000)]  # (K, N)
 MS = [1, 2, 4, 8]
 QTYPE, GROUP_K = 1, 128
 BS = 16 * GROUP_K + 128
-# DRAM bytes per decode launch of this sweep from one ncu capture (3,561,888,512 B over 113 launches), against
+# DRAM bytes per decode launch of this sweep from one ncu capture (3,561,665,024 B over 113 launches), against
 # 31.89 MB of algorithmic bytes per launch
 DECODE_TRAFFIC_PER_LAUNCH = 31.52e6
 METRIC = "Q4_1 FC decode weight GB/s"
