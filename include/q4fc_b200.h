@@ -136,6 +136,15 @@ int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq
             int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
             q4fc_stream_t stream);
 
+/* q4fc_fc_decode with the addition that follows the FC in the reference folded into the kernel's last step:
+ * y = fc(x) + addend, one fp32 add per output as llmops.iadd does (ops/op_misc.hpp:55-79) -- the bias
+ * (chatllama/main.py:166-167; ld_addend = 0: addend is one row of N values used for every row) or the residual
+ * stream (chatllama/main.py:356, 372; addend is [rows][ld_addend] and may be y itself).  rows <= 8; the
+ * stream-K flag is not accepted. */
+int q4fc_fc_decode_add(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                       int qtype, int group_k, int64_t N, float* y, int64_t ldy, const float* addend,
+                       int64_t ld_addend, void* ws, size_t ws_bytes, unsigned flags, q4fc_stream_t stream);
+
 /* ---- activations quantized once, used by several FCs ------------------------------------------------
  * In the reference every FC quantizes its input itself, so the output of one normalization is quantized
  * three times (q, k, v projections) or twice (gate, up) -- chatllama/main.py:344-368.  These entry points

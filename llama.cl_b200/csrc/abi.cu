@@ -336,6 +336,31 @@ int q4fc_fc_decode_q8(const void* xq, int64_t rows, int64_t K, const void* wq, i
                                     N, y, ldy, flags, static_cast<cudaStream_t>(stream), nullptr, 0, xq);
 }
 
+int q4fc_fc_decode_add(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
+                       int qtype, int group_k, int64_t N, float* y, int64_t ldy, const float* addend,
+                       int64_t ld_addend, void* ws, size_t ws_bytes, unsigned flags, q4fc_stream_t stream) {
+    if (int rc = check_fc_args("fc_decode_add", x, rows, K, ldx, wq, Ng, Kg, qtype, group_k, N, y, ldy)) return rc;
+    if (rows > kMaxDecodeRows) {
+        set_error("fc_decode_add: rows=%lld exceeds %d", (long long)rows, kMaxDecodeRows);
+        return Q4FC_ELIMIT;
+    }
+    if (flags & Q4FC_FLAG_STREAMK) {
+        set_error("fc_decode_add: Q4FC_FLAG_STREAMK is not available with an addend");
+        return Q4FC_EINVAL;
+    }
+    if (rows > 0 && N > 0 && (!addend || !aligned(addend, 4) || ld_addend < 0 || (ld_addend != 0 && ld_addend < N))) {
+        set_error("fc_decode_add: addend is null or misaligned, or 0 < ld_addend < N");
+        return Q4FC_EINVAL;
+    }
+    if (ws && !aligned(ws, 256)) {
+        set_error("fc_decode_add: workspace needs 256-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    return launch_fc_decode_cluster(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N,
+                                    y, ldy, flags, static_cast<cudaStream_t>(stream), ws, ws_bytes, nullptr, addend,
+                                    ld_addend);
+}
+
 int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
                     int qtype, int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
                     unsigned flags, q4fc_stream_t stream) {

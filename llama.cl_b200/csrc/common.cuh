@@ -63,7 +63,8 @@ int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uin
 // cluster form of the decode kernel (no global scratch)
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
-                             cudaStream_t s, void* ws = nullptr, size_t ws_bytes = 0, const void* xq = nullptr);
+                             cudaStream_t s, void* ws = nullptr, size_t ws_bytes = 0, const void* xq = nullptr,
+                             const float* addend = nullptr, int64_t addend_ld = 0);
 // RMS normalization fused with the quantizer (rmsnorm_quant.cu); writes the pre-quantized format
 int launch_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int rows, int64_t K, int64_t ldx,
                          const float* weight, float eps, float* y,

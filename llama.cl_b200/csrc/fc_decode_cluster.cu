@@ -38,9 +38,10 @@ int64_t pre_quant_min_values() {
 
 int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
-                             cudaStream_t s, void* ws, size_t ws_bytes, const void* xq) {
+                             cudaStream_t s, void* ws, size_t ws_bytes, const void* xq, const float* addend,
+                             int64_t addend_ld) {
     return launch_cluster_impl<false>(x, rows, K, ldx, wq, Ng, Kg, qtype, G, N, y, ldy, flags, s, nullptr, ws,
-                                      ws_bytes, xq);
+                                      ws_bytes, xq, addend, addend_ld);
 }
 
 }  // namespace q4fc

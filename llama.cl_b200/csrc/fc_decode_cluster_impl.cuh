@@ -93,6 +93,10 @@ struct ClusterParams {
     const int8_t* xq;
     const float* xsc;
     int64_t xq_stride;
+    // optional epilogue: y = fc(x) + addend (the reference's iadd of a bias or of the residual stream after the FC,
+    // chatllama/main.py:166-167, 356, 372).  addend_ld = 0: one row broadcast over the rows (bias); else row stride.
+    const float* addend;
+    int64_t addend_ld;
     // ---- N-split over several GPUs, joined by this kernel itself (world == 0: single GPU, fields unused).
     // Outputs travel as 8-byte "stamped" words: the fp32 value in the low half, the low 32 bits of the step
     // counter ("epoch") in the high half.  A 64-bit store is indivisible, so a reader that finds the current
@@ -518,6 +522,7 @@ __global__ void __launch_bounds__(kCThreads, 4) fc_decode_cluster_kernel(const C
             if (m < p.rows) {
                 float sum = 0.0f;
                 for (int q = 0; q < nsl; q++) sum += src[q * p.slot_f + m * 32 + lane];
+                if (n < p.N && p.addend != nullptr) sum = __fadd_rn(sum, p.addend[m * p.addend_ld + n]);
                 if (n < p.N) {
                     if constexpr (!TP) {
                         p.y[m * p.ldy + n] = sum;
@@ -629,7 +634,7 @@ template <bool TP>
 int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
                         int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags, cudaStream_t s,
                         const q4fc_tp_site* tp, void* ws = nullptr, size_t ws_bytes = 0,
-                        const void* xq_given = nullptr) {
+                        const void* xq_given = nullptr, const float* addend = nullptr, int64_t addend_ld = 0) {
     // a rank without columns still launches nothing: its peers count only the stripes that exist
     if (rows == 0 || N == 0) return Q4FC_OK;
     const DeviceInfo* di = device_info();
@@ -642,6 +647,7 @@ int launch_cluster_impl(const float* x, int rows, int64_t K, int64_t ldx, const 
     p.x = x, p.y = y, p.wq = wq;
     p.K = K, p.ldx = ldx, p.N = N, p.ldy = ldy;
     p.rows = rows, p.Ng = (int)Ng, p.Kg = (int)Kg;
+    p.addend = addend, p.addend_ld = addend_ld;
     p.world = 0, p.x_stamped = 0, p.col_off = 0, p.epoch = nullptr, p.status = nullptr;
     for (int i = 0; i < 8; i++) p.y_peer[i] = nullptr;
     if (tp) {

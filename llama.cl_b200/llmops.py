@@ -140,7 +140,7 @@ def FC_dynamic_quantize_x(input: torch.Tensor, group_k: int, scale: float = 1.0)
 
 def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_signed: bool = False,
            out: torch.Tensor | None = None, workspace: Workspace | None = None, pdl: bool = False,
-           path: str = "auto", prequant: bool = False) -> torch.Tensor:
+           path: str = "auto", prequant: bool = False, addend: torch.Tensor | None = None) -> torch.Tensor:
     """``y[b, m, :N] = quantized(input[b, m]) . W`` (ops/op_fc.hpp:286-426).
 
     input fp32 ``[B, M, K]``, wei_quantized int8 ``[Ng, Kg, block_bytes]`` ->
@@ -148,7 +148,9 @@ def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_s
     the prefill kernel), "decode", "streamk" (the decode kernel that reduces
     through the workspace) or "prefill".  ``prequant=True`` (decode kernel): quantize the activations in a
     small launch of their own whatever the size -- less total work when several FCs run side by side on
-    different streams; by default that happens only for large rows x K."""
+    different streams; by default that happens only for large rows x K.  ``addend`` (decode kernel, B*M <= 8):
+    fp32 ``[N]`` (a bias) or ``[B, M, N]`` (a residual; may be ``out``), added to the result inside the kernel
+    with one fp32 add per output, as the reference's ``llmops.iadd`` after the FC does."""
     _require_cuda(input, "input", torch.float32, 3)
     _require_cuda(wei_quantized, "wei_quantized", torch.int8, 3)
     if wei_quantized.device != input.device:
@@ -172,6 +174,21 @@ def fc_Q4A(input: torch.Tensor, wei_quantized: torch.Tensor, N: int, *, nibble_s
     if prequant:
         flags |= _cabi.FLAG_PREQUANT
     L = _cabi.lib()
+    if addend is not None:
+        _require_cuda(addend, "addend", torch.float32, addend.dim())
+        if rows > 8 or path in ("streamk", "prefill"):
+            raise RuntimeError("addend is folded into the decode kernel only (B*M <= 8, path auto or decode)")
+        if tuple(addend.shape) == (N,):
+            ld_add = 0
+        elif tuple(addend.shape) == (B, M, N) and addend.is_contiguous():
+            ld_add = N
+        else:
+            raise RuntimeError(f"addend: expected contiguous shape {(N,)} or {(B, M, N)}, got {tuple(addend.shape)}")
+        with torch.cuda.device(input.device):
+            _cabi.check(L.q4fc_fc_decode_add(input.data_ptr(), rows, K, K, wei_quantized.data_ptr(), Ng, Kg, q, G, N,
+                                             out.data_ptr(), N, addend.data_ptr(), ld_add, workspace.ptr,
+                                             workspace.nbytes, flags, _stream_ptr(input.device)), "fc_Q4A")
+        return out
     fn = {"auto": L.q4fc_fc, "decode": L.q4fc_fc_decode, "streamk": L.q4fc_fc_decode,
           "prefill": L.q4fc_fc_prefill}[path]
     with torch.cuda.device(input.device):

@@ -23,6 +23,9 @@ class llmop_fc_q4a:
         self.N = int(linear.weight.shape[0])
 
     def __call__(self, input: torch.Tensor, **kw) -> torch.Tensor:
+        if self.bias is not None and input.shape[0] * input.shape[1] <= 8 and kw.get("path", "auto") in ("auto", "decode"):
+            # the reference's llmops.iadd(out, bias), folded into the decode kernel (same single fp32 add)
+            return llmops.fc_Q4A(input, self.weight, self.N, addend=self.bias, **kw)
         out = llmops.fc_Q4A(input, self.weight, self.N, **kw)
         if self.bias is not None:
             out.add_(self.bias)  # the reference's llmops.iadd(out, bias)

@@ -575,3 +575,32 @@ def test_rmsnorm_quantize_matches_the_reference_rows(lib_built):
     assert np.array_equal(rd.cpu().numpy(), summed)
     with pytest.raises(RuntimeError):
         pkg.llmops.rmsnorm_quantize(torch.zeros(1, 1, 12, device="cuda"), torch.ones(12, device="cuda"), 1e-5, 32)
+
+
+@pytest.mark.parametrize("qname,G", [("q4_1", 128), ("q4_0", 32)])
+def test_fc_decode_with_addend(lib_built, qname, G):
+    """Bias or residual folded into the decode kernel: the same bytes as the FC followed by one fp32 add
+    (the reference's llmops.iadd), also in place on the output and behind the separate quantizing launch."""
+    import llama_cl_b200 as pkg
+
+    g = torch.Generator().manual_seed(41)
+    for rows, K, N in [(1, 4096, 1000), (8, 1024, 96), (4, 11008, 160)]:
+        W = (torch.randn(N, K, generator=g) * 0.02).cuda()
+        wq = pkg.llmops.offline_FC_quant_Q4A(W, qtype=qname, group_k=G)
+        x = torch.randn(1, rows, K, generator=g).cuda()
+        bias = torch.randn(N, generator=g).cuda()
+        res = torch.randn(1, rows, N, generator=g).cuda()
+        plain = pkg.llmops.fc_Q4A(x, wq, N, path="decode")
+        assert torch.equal(pkg.llmops.fc_Q4A(x, wq, N, addend=bias), plain + bias)
+        assert torch.equal(pkg.llmops.fc_Q4A(x, wq, N, addend=res), plain + res)
+        inplace = res.clone()
+        pkg.llmops.fc_Q4A(x, wq, N, addend=inplace, out=inplace)  # hidden = fc(x) + hidden
+        assert torch.equal(inplace, plain + res)
+
+        import types
+
+        lin = types.SimpleNamespace(weight=W, bias=bias)  # what llmop_fc_q4a takes: .weight, .bias
+        op = pkg.ops.llmop_fc_q4a(lin, qtype=qname, group_k=G)
+        assert torch.equal(op(x), plain + bias)
+    with pytest.raises(RuntimeError):
+        pkg.llmops.fc_Q4A(x, wq, N, addend=torch.zeros(N + 1, device="cuda"))
