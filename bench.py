@@ -642,6 +642,27 @@ def our_arm(args) -> None:
                 nbytes = Wp.numel() * 4 + outp.numel()
                 pk[f"g{G_}"] = {"ms": ms_, "gb_s": nbytes / (ms_ * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_ * 1e-3) / 1e9 / load_peaks()[0]}
             extras["pack_q4_1_11008x4096"] = pk
+            # packer over a whole Llama-7B FC weight set: 32 layers x {q, k, v, o: 4096x4096; gate, up: 11008x4096;
+            # down: 4096x11008}, one matrix after the other (every fp32 matrix is 64-180 MB: nothing stays in L2)
+            shapes_ = {(4096, 4096): 4 * 32, (11008, 4096): 2 * 32, (4096, 11008): 1 * 32}
+            mats_ = {sh: torch.randn(sh, generator=gen, device=dev, dtype=torch.float32) * 0.02 for sh in shapes_}
+            full = {}
+            for G_ in (32, 128):
+                outs_ = {sh: torch.empty(((sh[0] + 31) // 32, sh[1] // G_, 16 * G_ + 128), dtype=torch.int8, device=dev)
+                         for sh in shapes_}
+
+                def pack_all():
+                    for sh, cnt in shapes_.items():
+                        for _ in range(cnt):
+                            pkg.llmops.offline_FC_quant_Q4A(mats_[sh], qtype="q4_1", group_k=G_, out=outs_[sh])
+
+                ms_ = timed(pack_all, 3)
+                nbytes = sum(cnt * (mats_[sh].numel() * 4 + outs_[sh].numel()) for sh, cnt in shapes_.items())
+                full[f"g{G_}"] = {"ms": ms_, "gb_s": nbytes / (ms_ * 1e-3) / 1e9, "weights": sum(
+                    cnt * mats_[sh].numel() for sh, cnt in shapes_.items()),
+                    "frac_of_hbm_peak": nbytes / (ms_ * 1e-3) / 1e9 / load_peaks()[0]}
+            extras["pack_q4_1_llama7b_fc_set_224_matrices"] = full
+            del mats_
             del Wp
         except Exception as e:
             extras = {"error": str(e)}
