@@ -5,7 +5,8 @@
  * below are what a binding of that project's FC ops would call instead of its
  * CPU code.  Plain pointers and sizes only; every pointer is a DEVICE pointer
  * unless stated otherwise; every call is asynchronous on `stream` and
- * allocates nothing.  All functions return 0 on success or a Q4FC_E* code and
+ * allocates nothing (the two exceptions, q4fc_tp_arena_create / _open, say
+ * so).  All functions return 0 on success or a Q4FC_E* code and
  * never throw or abort; q4fc_last_error() gives the detail text of the last
  * failure on the calling thread.
  *
