@@ -23,7 +23,8 @@ def _worker(rank, world, initfile, result_q):
 
         ok = True
         for (N, K, rows, qname, G) in [(4096, 4096, 1, "q4_1", 128), (11008, 4096, 4, "q4_1", 128),
-                                       (4096, 11008, 8, "q4_1", 32), (32000, 4096, 1, "q4_0", 32)]:
+                                       (4096, 11008, 8, "q4_1", 32), (32000, 4096, 1, "q4_0", 32),
+                                       (11008, 4096, 192, "q4_0", 32)]:  # the last: prefill kernel per shard
             g = torch.Generator().manual_seed(N + K + rows)
             W = (torch.randn(N, K, generator=g) * 0.02).to(dev)
             x = torch.randn(1, rows, K, generator=g).to(dev)
