@@ -63,16 +63,15 @@ enum {
      * write this call's weights. */
     Q4FC_FLAG_PDL = 2u,
     /* q4fc_fc_decode only: use the stream-K kernel (one contiguous byte run
-     * per CTA, partial sums through the workspace) instead of the default
-     * cluster kernel (partial sums through distributed shared memory, no
-     * workspace needed).  Same results within rounding of the fp32 sums. */
+     * per CTA, weights staged in registers, partial sums through the workspace)
+     * instead of the default kernel (weights staged in a shared-memory ring by
+     * bulk copies, partial sums through shared memory, no workspace needed).
+     * Same results within rounding of the fp32 sums. */
     Q4FC_FLAG_STREAMK = 4u,
     /* q4fc_fc_decode with a workspace: always quantize the activations in a small launch of their own in
      * front of the FC kernel (by default only for large rows x K).  The FC kernel otherwise quantizes
-     * them itself, every cluster its own copy: the shortest path for one call at a time, but repeated
-     * work that competes for the SMs when several FCs run side by side on different streams.  Codes and
-     * scales are the same bit for bit; the kernel then also splits K over clusters of 4 instead of 8, so
-     * outputs agree within the rounding of the fp32 sums. */
+     * them itself, every CTA its own copy: the shortest path for one call at a time, but repeated work.
+     * Codes, scales and outputs are the same bit for bit. */
     Q4FC_FLAG_PREQUANT = 8u
 };
 
@@ -145,6 +144,27 @@ int q4fc_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq
 int q4fc_fc_decode_add(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
                        int qtype, int group_k, int64_t N, float* y, int64_t ldy, const float* addend,
                        int64_t ld_addend, void* ws, size_t ws_bytes, unsigned flags, q4fc_stream_t stream);
+
+/* Several FCs that read the same input, as one launch: the q, k and v projections of an attention block
+ * (chatllama/main.py:348-350), or gate and up of the MLP (chatllama/main.py:365-367) -- in the reference three
+ * and two calls of fc_Q4A on one tensor.  Every job is one packed weight tensor of the same block type and the
+ * same Kg with its own output (and optional addend, as q4fc_fc_decode_add); the stripes of all jobs are dealt
+ * over the SMs as one list, so short outputs share a launch instead of each paying its own start and end.
+ * njobs 1..4, rows <= 8.  x: fp32 [rows][ldx], or NULL with xq != NULL: a buffer made by q4fc_quant_x_q8 /
+ * q4fc_rmsnorm_quant / q4fc_silu_mul_quant (then ldx is ignored).  Each output equals what q4fc_fc_decode /
+ * q4fc_fc_decode_q8 gives for that job alone, bit for bit. */
+typedef struct q4fc_fc_job {
+    const void* wq;      /* packed [Ng][Kg][BS] */
+    int64_t Ng;
+    int64_t N;           /* N <= 32 * Ng */
+    float* y;            /* fp32 [rows][ldy] */
+    int64_t ldy;
+    const float* addend; /* NULL, or as in q4fc_fc_decode_add */
+    int64_t ld_addend;
+} q4fc_fc_job;
+int q4fc_fc_decode_multi(const float* x, const void* xq, int64_t rows, int64_t K, int64_t ldx, int64_t Kg, int qtype,
+                         int group_k, const q4fc_fc_job* jobs, int njobs, void* ws, size_t ws_bytes, unsigned flags,
+                         q4fc_stream_t stream);
 
 /* ---- activations quantized once, used by several FCs ------------------------------------------------
  * In the reference every FC quantizes its input itself, so the output of one normalization is quantized
@@ -251,7 +271,9 @@ int q4fc_fc_decode_tp(const void* x, int64_t rows, int64_t K, int64_t ldx, const
                       q4fc_stream_t stream);
 
 /* Reads and clears the device status word kept at the start of a workspace
- * (host-synchronous: waits for `stream`).  Returns Q4FC_OK or Q4FC_EDEVICE. */
+ * (host-synchronous: waits for `stream`).  ws = NULL reads the word that decode
+ * calls made without a workspace share (one per device).  Returns Q4FC_OK or
+ * Q4FC_EDEVICE (a bounded wait inside a kernel ran out; its results are invalid). */
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream);
 
 #if defined(__GNUC__)

@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -35,6 +36,8 @@ const DeviceInfo* device_info() {
         set_error("no current CUDA device");
         return nullptr;
     }
+    static std::mutex m;  // first calls on a device may come from several host threads
+    std::lock_guard<std::mutex> lk(m);
     if (!ready[dev]) {
         int sms = 0, smem = 0;
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
@@ -242,7 +245,7 @@ int q4fc_fc_decode(const float* x, int64_t rows, int64_t K, int64_t ldx, const v
     if (flags & Q4FC_FLAG_STREAMK)
         return launch_fc_decode(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y,
                                 ldy, ws, ws_bytes, flags, static_cast<cudaStream_t>(stream));
-    return launch_fc_decode_cluster(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N,
+    return launch_fc_decode_ring(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N,
                                     y, ldy, flags, static_cast<cudaStream_t>(stream), ws, ws_bytes);
 }
 
@@ -332,7 +335,7 @@ int q4fc_fc_decode_q8(const void* xq, int64_t rows, int64_t K, const void* wq, i
         set_error("fc_decode_q8: Q4FC_FLAG_STREAMK is not available for pre-quantized activations");
         return Q4FC_EINVAL;
     }
-    return launch_fc_decode_cluster(nullptr, (int)rows, K, K, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k,
+    return launch_fc_decode_ring(nullptr, (int)rows, K, K, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k,
                                     N, y, ldy, flags, static_cast<cudaStream_t>(stream), nullptr, 0, xq);
 }
 
@@ -356,9 +359,52 @@ int q4fc_fc_decode_add(const float* x, int64_t rows, int64_t K, int64_t ldx, con
         set_error("fc_decode_add: workspace needs 256-byte alignment");
         return Q4FC_EALIGN;
     }
-    return launch_fc_decode_cluster(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N,
+    return launch_fc_decode_ring(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N,
                                     y, ldy, flags, static_cast<cudaStream_t>(stream), ws, ws_bytes, nullptr, addend,
                                     ld_addend);
+}
+
+int q4fc_fc_decode_multi(const float* x, const void* xq, int64_t rows, int64_t K, int64_t ldx, int64_t Kg, int qtype,
+                         int group_k, const q4fc_fc_job* jobs, int njobs, void* ws, size_t ws_bytes, unsigned flags,
+                         q4fc_stream_t stream) {
+    if (!jobs || njobs < 1 || njobs > 4) {
+        set_error("fc_decode_multi: null jobs or njobs=%d outside 1..4", njobs);
+        return Q4FC_EINVAL;
+    }
+    if ((x == nullptr) == (xq == nullptr)) {
+        set_error("fc_decode_multi: exactly one of x and xq must be given");
+        return Q4FC_EINVAL;
+    }
+    if (xq) {
+        if (int rc = check_xq_args("fc_decode_multi", rows, K, group_k, xq)) return rc;
+        ldx = K;
+    }
+    if (rows > kMaxDecodeRows) {
+        set_error("fc_decode_multi: rows=%lld exceeds %d", (long long)rows, kMaxDecodeRows);
+        return Q4FC_ELIMIT;
+    }
+    if (flags & Q4FC_FLAG_STREAMK) {
+        set_error("fc_decode_multi: Q4FC_FLAG_STREAMK is not available for several weight tensors");
+        return Q4FC_EINVAL;
+    }
+    if (ws && !aligned(ws, 256)) {
+        set_error("fc_decode_multi: workspace needs 256-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    for (int i = 0; i < njobs; i++) {
+        const q4fc_fc_job& jb = jobs[i];
+        // with codes as input they stand in for x in the shared argument checks (pointer non-null, 4-byte aligned)
+        if (int rc = check_fc_args("fc_decode_multi", x ? x : static_cast<const float*>(xq), rows, K, ldx, jb.wq, jb.Ng,
+                                   Kg, qtype, group_k, jb.N, jb.y, jb.ldy))
+            return rc;
+        if (rows > 0 && jb.N > 0 && jb.addend &&
+            (!aligned(jb.addend, 4) || jb.ld_addend < 0 || (jb.ld_addend != 0 && jb.ld_addend < jb.N))) {
+            set_error("fc_decode_multi: job %d: addend is misaligned, or 0 < ld_addend < N", i);
+            return Q4FC_EINVAL;
+        }
+    }
+    return launch_fc_decode_ring_multi(x, (int)rows, K, ldx, Kg, qtype, group_k, jobs, njobs, flags,
+                                       static_cast<cudaStream_t>(stream), ws, ws_bytes, xq);
 }
 
 int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
@@ -484,15 +530,15 @@ int q4fc_fc_decode_tp(const void* x, int64_t rows, int64_t K, int64_t ldx, const
         set_error("fc_decode_tp: rows=%lld exceeds %d", (long long)rows, kMaxDecodeRows);
         return Q4FC_ELIMIT;
     }
-    return launch_fc_decode_cluster_tp(static_cast<const float*>(x), (int)rows, K, ldx,
+    return launch_fc_decode_ring_tp(static_cast<const float*>(x), (int)rows, K, ldx,
                                        static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, ldy, flags,
                                        static_cast<cudaStream_t>(stream), site);
 }
 
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream) {
     if (!ws) {
-        set_error("check_status: null workspace");
-        return Q4FC_EWORKSPACE;
+        ws = ring_status_word();
+        if (!ws) return Q4FC_ECUDA;
     }
     int status = 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -60,11 +60,17 @@ size_t decode_prequant_offset();
 int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
                      int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes, unsigned flags,
                      cudaStream_t s);
-// cluster form of the decode kernel (no global scratch)
-int launch_fc_decode_cluster(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
-                             int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags,
-                             cudaStream_t s, void* ws = nullptr, size_t ws_bytes = 0, const void* xq = nullptr,
-                             const float* addend = nullptr, int64_t addend_ld = 0);
+// ring form of the decode kernel (bulk copies into a shared-memory ring; no global scratch): fc_decode_ring*.cu
+int launch_fc_decode_ring(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
+                          int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags, cudaStream_t s,
+                          void* ws = nullptr, size_t ws_bytes = 0, const void* xq = nullptr,
+                          const float* addend = nullptr, int64_t addend_ld = 0);
+// several weight tensors on one input in one launch
+int launch_fc_decode_ring_multi(const float* x, int rows, int64_t K, int64_t ldx, int64_t Kg, int qtype, int G,
+                                const q4fc_fc_job* jobs, int njobs, unsigned flags, cudaStream_t s, void* ws,
+                                size_t ws_bytes, const void* xq);
+// device address of the status word used by launches without a workspace (current device), or nullptr
+int* ring_status_word();
 // RMS normalization fused with the quantizer (rmsnorm_quant.cu); writes the pre-quantized format
 int launch_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int rows, int64_t K, int64_t ldx,
                          const float* weight, float eps, float* y,
@@ -73,9 +79,8 @@ int launch_rmsnorm_quant(const float* x, const float* residual, float* sum_out, 
 size_t quant_pre_bytes(int64_t rows, int64_t K, int G);
 int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, bool want_isum, int8_t* codes,
                        float* sc, bool pdl, cudaStream_t s);
-int64_t pre_quant_min_values();
 // the same kernel with outputs stored, epoch-stamped, into every rank's buffer (tp->y_peer)
-int launch_fc_decode_cluster_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
+int launch_fc_decode_ring_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                                 int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,
                                 const q4fc_tp_site* tp);
 // step barrier and stream-side wait of the N-split over several GPUs
@@ -83,7 +88,6 @@ int launch_tp_step_begin(unsigned long long* epoch, unsigned long long* const* b
                          const unsigned long long* barrier_local, int world, int* status, cudaStream_t s);
 int launch_tp_collect(const unsigned long long* src, int64_t rows, int64_t N, int64_t ld, float* dst, int64_t ldd,
                       const unsigned long long* epoch, int* status, cudaStream_t s);
-int choose_cluster_count(int64_t Ng, int64_t nc_cap);
 size_t prefill_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int G);
 int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                       int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,

@@ -42,6 +42,11 @@ class HostFC:
         self.max_rows = max_rows
         self.use_graph = bool(graph)
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        if self.fc_kwargs.get("workspace") is None:
+            # captured graphs hold the workspace's address: own one, sized once for the largest call
+            with torch.cuda.device(dev):
+                need = int(_cabi.lib().q4fc_fc_workspace_bytes(max_rows, self.K, self.N, self.qtype, self.G))
+            self.fc_kwargs["workspace"] = llmops.Workspace(need, dev)
 
     def x_staging(self, M: int) -> torch.Tensor:
         """The pinned input buffer ``[1, M, K]`` a call with ``M`` rows reads: writing the activations

@@ -23,7 +23,8 @@ from . import _cabi
 from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, FLAG_STREAMK, Q4_0, Q4_1
 
 __all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
-           "fc_workspace", "Workspace"]
+           "fc_workspace", "Workspace", "fc_Q4A_multi", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize",
+           "QuantizedActivations"]
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -64,16 +65,25 @@ class Workspace:
 
 
 _workspaces: dict = {}
+_retired: list = []  # replaced workspaces stay allocated: CUDA graphs captured earlier hold their raw pointers
 
 
 def fc_workspace(rows: int, K: int, N: int, qtype: int, group_k: int, device: torch.device) -> Workspace:
-    """Cached workspace for (device, current stream), grown on demand."""
+    """Cached workspace for (device, current stream), grown on demand.
+
+    A decode call is sized for 8 rows whatever it asks for, so that the row count of later calls on the stream
+    does not replace the workspace; when a larger one is needed all the same, the old one is kept alive (never
+    freed), because graphs captured with it would otherwise replay into freed memory.  Objects that capture
+    graphs (``host.HostFC`` and friends) own a workspace sized for their largest call instead of using this
+    cache."""
     with torch.cuda.device(device):
-        need = int(_cabi.lib().q4fc_fc_workspace_bytes(rows, K, N, qtype, group_k))
+        need = int(_cabi.lib().q4fc_fc_workspace_bytes(max(rows, 8) if rows <= 8 else rows, K, N, qtype, group_k))
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.nbytes < need:
+        if ws is not None:
+            _retired.append(ws)
         ws = Workspace(need, device)
         _workspaces[key] = ws
     return ws
@@ -299,12 +309,78 @@ def fc_Q4A_q8(xq: QuantizedActivations, wei_quantized: torch.Tensor, N: int, *, 
         _require_cuda(out, "out", torch.float32, 3)
         if tuple(out.shape) != (xq.B, xq.M, N):
             raise RuntimeError(f"out: expected shape {(xq.B, xq.M, N)}, got {tuple(out.shape)}")
+    if xq.signed and q != Q4_0:
+        # the group-sum slot then holds the bits of 8 * (sum of codes), which a Q4_1 kernel would read as a float
+        raise RuntimeError("activations quantized with nibble_signed=True serve Q4_0 weights only")
     flags = (FLAG_PDL if pdl else 0) | (FLAG_NIBBLE_SIGNED if (xq.signed and q == Q4_0) else 0)
     with torch.cuda.device(wei_quantized.device):
         _cabi.check(_cabi.lib().q4fc_fc_decode_q8(xq.buf.data_ptr(), xq.rows, xq.K, wei_quantized.data_ptr(), Ng, Kg,
                                                   q, G, N, out.data_ptr(), N, flags,
                                                   _stream_ptr(wei_quantized.device)), "fc_Q4A_q8")
     return out
+
+
+def fc_Q4A_multi(input, weights, Ns, *, outs=None, addends=None, workspace: Workspace | None = None,
+                 pdl: bool = False, nibble_signed: bool = False):
+    """Several ``fc_Q4A`` on one input as ONE launch (``q4fc_fc_decode_multi``): the q/k/v projections, or
+    gate/up -- three and two calls on the same tensor in the reference (chatllama/main.py:348-350, 365-367).
+
+    ``input``: fp32 ``[B, M, K]`` with ``B*M <= 8``, or ``QuantizedActivations``.  ``weights``: up to four packed
+    tensors of one block type and the same ``Kg``; ``Ns``: their output widths.  Returns the list of outputs,
+    each bit-equal to the single call's."""
+    prequantized = isinstance(input, QuantizedActivations)
+    if prequantized:
+        B, M, K, dev = input.B, input.M, input.K, input.buf.device
+    else:
+        _require_cuda(input, "input", torch.float32, 3)
+        B, M, K = input.shape
+        dev = input.device
+    rows = B * M
+    _check_rows(rows)
+    if not 1 <= len(weights) <= 4 or len(Ns) != len(weights):
+        raise RuntimeError("fc_Q4A_multi: one to four weight tensors, with one N each")
+    q = G = Kg = None
+    jobs = (_cabi.FcJob * len(weights))()
+    outs = list(outs) if outs is not None else [None] * len(weights)
+    addends = list(addends) if addends is not None else [None] * len(weights)
+    for i, (w, N) in enumerate(zip(weights, Ns)):
+        _require_cuda(w, f"weights[{i}]", torch.int8, 3)
+        qi, Gi = _cabi.infer_variant(w.shape[2])
+        if q is None:
+            q, G, Kg = qi, Gi, int(w.shape[1])
+        elif (qi, Gi, int(w.shape[1])) != (q, G, Kg):
+            raise RuntimeError("fc_Q4A_multi: the weight tensors differ in block type or K")
+        N = int(N)
+        if outs[i] is None:
+            outs[i] = torch.empty((B, M, N), dtype=torch.float32, device=dev)
+        else:
+            _require_cuda(outs[i], f"outs[{i}]", torch.float32, 3)
+            if tuple(outs[i].shape) != (B, M, N):
+                raise RuntimeError(f"outs[{i}]: expected shape {(B, M, N)}, got {tuple(outs[i].shape)}")
+        jobs[i].wq, jobs[i].Ng, jobs[i].N = w.data_ptr(), int(w.shape[0]), N
+        jobs[i].y, jobs[i].ldy = outs[i].data_ptr(), N
+        a = addends[i]
+        if a is not None:
+            _require_cuda(a, f"addends[{i}]", torch.float32, a.dim())
+            if tuple(a.shape) == (N,):
+                jobs[i].ld_addend = 0
+            elif tuple(a.shape) == (B, M, N):
+                jobs[i].ld_addend = N
+            else:
+                raise RuntimeError(f"addends[{i}]: expected shape {(N,)} or {(B, M, N)}, got {tuple(a.shape)}")
+            jobs[i].addend = a.data_ptr()
+    if (K + G - 1) // G != Kg:
+        raise RuntimeError(f"fc_Q4A_multi: K={K} does not match the weights' {Kg} groups of {G}")
+    signed = nibble_signed or (prequantized and input.signed)
+    if prequantized and input.signed and q != Q4_0:
+        raise RuntimeError("activations quantized with nibble_signed=True serve Q4_0 weights only")
+    flags = (FLAG_PDL if pdl else 0) | (FLAG_NIBBLE_SIGNED if (signed and q == Q4_0) else 0)
+    with torch.cuda.device(dev):
+        _cabi.check(_cabi.lib().q4fc_fc_decode_multi(
+            None if prequantized else input.data_ptr(), input.buf.data_ptr() if prequantized else None, rows, K, K,
+            Kg, q, G, jobs, len(weights), workspace.ptr if workspace is not None else None,
+            workspace.nbytes if workspace is not None else 0, flags, _stream_ptr(dev)), "fc_Q4A_multi")
+    return outs
 
 
 def fc_Q4A2(input, wei_quantized, N):
