@@ -152,7 +152,8 @@ int q4fc_fc_decode_add(const float* x, int64_t rows, int64_t K, int64_t ldx, con
  * over the SMs as one list, so short outputs share a launch instead of each paying its own start and end.
  * njobs 1..4, rows <= 8.  x: fp32 [rows][ldx], or NULL with xq != NULL: a buffer made by q4fc_quant_x_q8 /
  * q4fc_rmsnorm_quant / q4fc_silu_mul_quant (then ldx is ignored).  Each output equals what q4fc_fc_decode /
- * q4fc_fc_decode_q8 gives for that job alone, bit for bit. */
+ * q4fc_fc_decode_q8 gives for that job alone, within the rounding of the fp32 sums (the jobs' stripes are
+ * cut over the SMs differently than a single call's). */
 typedef struct q4fc_fc_job {
     const void* wq;      /* packed [Ng][Kg][BS] */
     int64_t Ng;
@@ -164,6 +165,26 @@ typedef struct q4fc_fc_job {
 } q4fc_fc_job;
 int q4fc_fc_decode_multi(const float* x, const void* xq, int64_t rows, int64_t K, int64_t ldx, int64_t Kg, int qtype,
                          int group_k, const q4fc_fc_job* jobs, int njobs, void* ws, size_t ws_bytes, unsigned flags,
+                         q4fc_stream_t stream);
+
+/* A batch of independent FCs as ONE launch: up to 16 calls of one block type, each with its own weights, output
+ * and pre-quantized input (calls may share an input: pass the same xq pointer).  The reference runs such calls
+ * one after the other (every fc_Q4A of ops/perf_ops.py:239-242, or of a model step, is a call of its own); here
+ * the stripes of all calls are dealt over the SMs as one list of about equal bytes per SM, so the whole batch
+ * streams without a kernel boundary in it -- on B200 a single 9 MB FC is over in the time a launch takes to
+ * start and end, while sixteen of them in one launch run at the pace of the memory system.  Every output is
+ * what q4fc_fc_decode_q8 gives for that call alone, within the rounding of the fp32 sums.  rows <= 8. */
+typedef struct q4fc_fc_call {
+    const void* xq;      /* q4fc_xq_bytes(rows, K, group_k) bytes made by q4fc_quant_x_q8 / q4fc_rmsnorm_quant / ... */
+    int64_t rows, K;
+    const void* wq;      /* packed [Ng][Kg][BS] */
+    int64_t Ng, Kg, N;
+    float* y;            /* fp32 [rows][ldy] */
+    int64_t ldy;
+    const float* addend; /* NULL, or as in q4fc_fc_decode_add */
+    int64_t ld_addend;
+} q4fc_fc_call;
+int q4fc_fc_decode_batch(const q4fc_fc_call* calls, int ncalls, int qtype, int group_k, unsigned flags,
                          q4fc_stream_t stream);
 
 /* ---- activations quantized once, used by several FCs ------------------------------------------------

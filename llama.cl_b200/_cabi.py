@@ -22,7 +22,7 @@ SYMBOLS = (
     "q4fc_version", "q4fc_strerror", "q4fc_last_error", "q4fc_block_bytes", "q4fc_infer_variant",
     "q4fc_pack", "q4fc_dequant", "q4fc_quant_x", "q4fc_fc_workspace_bytes", "q4fc_fc_workspace_init",
     "q4fc_fc_decode", "q4fc_fc_prefill", "q4fc_fc", "q4fc_fc_check_status", "q4fc_fc_decode_noalloc",
-    "q4fc_fc_decode_add", "q4fc_fc_decode_multi",
+    "q4fc_fc_decode_add", "q4fc_fc_decode_multi", "q4fc_fc_decode_batch",
     "q4fc_tp_arena_create", "q4fc_tp_arena_open", "q4fc_tp_arena_close", "q4fc_tp_arena_destroy",
     "q4fc_tp_step_begin", "q4fc_tp_collect", "q4fc_fc_decode_tp", "q4fc_tp_site_bytes",
     "q4fc_xq_bytes", "q4fc_quant_x_q8", "q4fc_rmsnorm_quant", "q4fc_add_rmsnorm_quant", "q4fc_fc_decode_q8",
@@ -48,6 +48,23 @@ class FcJob(C.Structure):
     _fields_ = [
         ("wq", C.c_void_p),
         ("Ng", C.c_int64),
+        ("N", C.c_int64),
+        ("y", C.c_void_p),
+        ("ldy", C.c_int64),
+        ("addend", C.c_void_p),
+        ("ld_addend", C.c_int64),
+    ]
+
+
+class FcCall(C.Structure):
+    """``q4fc_fc_call`` of include/q4fc_b200.h."""
+    _fields_ = [
+        ("xq", C.c_void_p),
+        ("rows", C.c_int64),
+        ("K", C.c_int64),
+        ("wq", C.c_void_p),
+        ("Ng", C.c_int64),
+        ("Kg", C.c_int64),
         ("N", C.c_int64),
         ("y", C.c_void_p),
         ("ldy", C.c_int64),
@@ -86,6 +103,7 @@ def lib() -> C.CDLL:
         getattr(L, name).argtypes = fc_args
     L.q4fc_fc_decode_add.argtypes = [vp, i64, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, vp, i64, vp, sz, u32, vp]
     L.q4fc_fc_decode_multi.argtypes = [vp, vp, i64, i64, i64, i64, i32, i32, C.POINTER(FcJob), i32, vp, sz, u32, vp]
+    L.q4fc_fc_decode_batch.argtypes = [C.POINTER(FcCall), i32, i32, i32, u32, vp]
     L.q4fc_fc_check_status.argtypes = [vp, vp]
     L.q4fc_fc_decode_noalloc.argtypes = [vp, i64, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, u32, vp]
     L.q4fc_xq_bytes.restype = sz

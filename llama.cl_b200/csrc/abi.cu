@@ -407,6 +407,31 @@ int q4fc_fc_decode_multi(const float* x, const void* xq, int64_t rows, int64_t K
                                        static_cast<cudaStream_t>(stream), ws, ws_bytes, xq);
 }
 
+int q4fc_fc_decode_batch(const q4fc_fc_call* calls, int ncalls, int qtype, int group_k, unsigned flags,
+                         q4fc_stream_t stream) {
+    if (!calls || ncalls < 1 || ncalls > 16) {
+        set_error("fc_decode_batch: null calls or ncalls=%d outside 1..16", ncalls);
+        return Q4FC_EINVAL;
+    }
+    if (flags & Q4FC_FLAG_STREAMK) {
+        set_error("fc_decode_batch: Q4FC_FLAG_STREAMK is not available for a batch");
+        return Q4FC_EINVAL;
+    }
+    for (int i = 0; i < ncalls; i++) {
+        const q4fc_fc_call& c = calls[i];
+        if (int rc = check_xq_args("fc_decode_batch", c.rows, c.K, group_k, c.xq)) return rc;
+        if (int rc = check_fc_args("fc_decode_batch", static_cast<const float*>(c.xq), c.rows, c.K, c.K, c.wq, c.Ng, c.Kg,
+                                   qtype, group_k, c.N, c.y, c.ldy))
+            return rc;
+        if (c.rows > 0 && c.N > 0 && c.addend &&
+            (!aligned(c.addend, 4) || c.ld_addend < 0 || (c.ld_addend != 0 && c.ld_addend < c.N))) {
+            set_error("fc_decode_batch: call %d: addend is misaligned, or 0 < ld_addend < N", i);
+            return Q4FC_EINVAL;
+        }
+    }
+    return launch_fc_decode_ring_batch(calls, ncalls, qtype, group_k, flags, static_cast<cudaStream_t>(stream));
+}
+
 int q4fc_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const void* wq, int64_t Ng, int64_t Kg,
                     int qtype, int group_k, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
                     unsigned flags, q4fc_stream_t stream) {

@@ -69,6 +69,8 @@ int launch_fc_decode_ring(const float* x, int rows, int64_t K, int64_t ldx, cons
 int launch_fc_decode_ring_multi(const float* x, int rows, int64_t K, int64_t ldx, int64_t Kg, int qtype, int G,
                                 const q4fc_fc_job* jobs, int njobs, unsigned flags, cudaStream_t s, void* ws,
                                 size_t ws_bytes, const void* xq);
+// a batch of independent FCs on pre-quantized inputs in one launch
+int launch_fc_decode_ring_batch(const q4fc_fc_call* calls, int ncalls, int qtype, int G, unsigned flags, cudaStream_t s);
 // device address of the status word used by launches without a workspace (current device), or nullptr
 int* ring_status_word();
 // RMS normalization fused with the quantizer (rmsnorm_quant.cu); writes the pre-quantized format

@@ -19,10 +19,6 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// (float)i for |i| < 2^22 without the quarter-rate cvt: 0x4B400000 is 1.5 * 2^23, where one ulp is 1, so adding
-// i to the bit pattern adds i to the value, and the subtraction is exact.
-__device__ __forceinline__ float exact_i2f(int i) { return __int_as_float(0x4B400000 + i) - 12582912.0f; }
-
 // One warp quantizes 128 consecutive k of ROWS rows: lane l holds v[m][0..3] = x[m][k0 + 4l .. 4l+3].
 // A K group spans SEG = G/4 lanes.  `len` = valid values of this lane's group (0: the group does not exist),
 // `body` = len rounded down to 8 (the reference's vector body rounds half to even, its scalar tail half away
@@ -92,44 +88,90 @@ __device__ __forceinline__ void q8_quantize_rows(const float (&v)[ROWS][4], int 
 //   codes  this lane's activation row g at the block's first k, plus 8t: 8 codes per set at +32j
 //   sc     the block's 16 floats: (scale, aux) of rows 0..7
 // The weight columns sit on the 16-row side of the MMA, the activation rows on its 8-column side; the k order
-// inside a set is permuted the same way on both operands (low nibbles = k 8t..8t+3, high = 8t+4..8t+7).
-// acc[c][mi] belongs to column 4g+c, row 2t+mi.
+// is permuted the same way on both operands.  acc[c][mi] belongs to column 4g+c, row 2t+mi.
+//
+// Group 128 (four sets): the low nibbles of two sets fill one MMA (w & 0x0F0F0F0F), the high nibbles of the
+// same two sets another one, left in place (w & 0xF0F0F0F0 = 16 x nibble, still a u8), so a word costs two
+// logic operations instead of three; the two exact integer sums meet in fp32: I = IL + IH / 16, exact because
+// IH is a multiple of 16 and everything stays below 2^24.  The integer ALU is the scarce pipe of this kernel;
+// the conversions (XU pipe) and the extra FMA are free by comparison.
+// Group 32 (one set): low nibbles in the first half of the MMA's k, shifted high nibbles in the second.
 template <int G, int QTYPE, bool SIGNED>
 __device__ __forceinline__ void block_accumulate(const uint4 (&q)[G / 32], uint2 wd, uint2 wm, const uint8_t* codes,
                                                  bool row_live, const float* sc, int t, float (&acc)[4][2]) {
     constexpr int SETS = G / 32;
-    // two accumulator chains per tile (even / odd sets) halve the dependent-MMA latency
-    int ia[4] = {0, 0, 0, 0}, ib[4] = {0, 0, 0, 0}, ja[4] = {0, 0, 0, 0}, jb[4] = {0, 0, 0, 0};
+    float fI[4][2];
+    const float4 s4 = *reinterpret_cast<const float4*>(sc + t * 4);  // scale, aux of rows 2t and 2t+1
+    const float xs[2] = {s4.x, s4.z};
+    const float gs[2] = {s4.y, s4.w};
+    if constexpr (SETS == 4) {
+        constexpr uint32_t kHiMask = 0xF0F0F0F0u;
+        int il0[4] = {0, 0, 0, 0}, il1[4] = {0, 0, 0, 0}, ih0[4] = {0, 0, 0, 0}, ih1[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int j = 0; j < SETS; j++) {
-        uint2 xb = make_uint2(0u, 0u);
-        if (row_live) xb = *reinterpret_cast<const uint2*>(codes + 32 * j);
-        uint32_t l0 = q[j].x & kNibMask, l1 = q[j].y & kNibMask, l2 = q[j].z & kNibMask, l3 = q[j].w & kNibMask;
-        uint32_t h0 = (q[j].x >> 4) & kNibMask, h1 = (q[j].y >> 4) & kNibMask, h2 = (q[j].z >> 4) & kNibMask,
-                 h3 = (q[j].w >> 4) & kNibMask;
-        if (SIGNED) {
-            l0 ^= 0x08080808u, l1 ^= 0x08080808u, l2 ^= 0x08080808u, l3 ^= 0x08080808u;
-            h0 ^= 0x08080808u, h1 ^= 0x08080808u, h2 ^= 0x08080808u, h3 ^= 0x08080808u;
+        for (int pr = 0; pr < 2; pr++) {
+            const uint4 qa = q[2 * pr], qb = q[2 * pr + 1];
+            uint2 xa = make_uint2(0u, 0u), xb = make_uint2(0u, 0u);
+            if (row_live) {
+                xa = *reinterpret_cast<const uint2*>(codes + 64 * pr);
+                xb = *reinterpret_cast<const uint2*>(codes + 64 * pr + 32);
+            }
+            uint32_t la0 = qa.x & kNibMask, la1 = qa.y & kNibMask, la2 = qa.z & kNibMask, la3 = qa.w & kNibMask;
+            uint32_t lb0 = qb.x & kNibMask, lb1 = qb.y & kNibMask, lb2 = qb.z & kNibMask, lb3 = qb.w & kNibMask;
+            uint32_t ha0 = qa.x & kHiMask, ha1 = qa.y & kHiMask, ha2 = qa.z & kHiMask, ha3 = qa.w & kHiMask;
+            uint32_t hb0 = qb.x & kHiMask, hb1 = qb.y & kHiMask, hb2 = qb.z & kHiMask, hb3 = qb.w & kHiMask;
+            if (SIGNED) {
+                la0 ^= 0x08080808u, la1 ^= 0x08080808u, la2 ^= 0x08080808u, la3 ^= 0x08080808u;
+                lb0 ^= 0x08080808u, lb1 ^= 0x08080808u, lb2 ^= 0x08080808u, lb3 ^= 0x08080808u;
+                ha0 ^= 0x80808080u, ha1 ^= 0x80808080u, ha2 ^= 0x80808080u, ha3 ^= 0x80808080u;
+                hb0 ^= 0x80808080u, hb1 ^= 0x80808080u, hb2 ^= 0x80808080u, hb3 ^= 0x80808080u;
+            }
+            mma_u8s8(il0, la0, la1, lb0, lb1, xa.x, xb.x);
+            mma_u8s8(il1, la2, la3, lb2, lb3, xa.x, xb.x);
+            mma_u8s8(ih0, ha0, ha1, hb0, hb1, xa.y, xb.y);
+            mma_u8s8(ih1, ha2, ha3, hb2, hb3, xa.y, xb.y);
         }
-        if (j & 1) {
-            mma_u8s8(ja, l0, l1, h0, h1, xb.x, xb.y);
-            mma_u8s8(jb, l2, l3, h2, h3, xb.x, xb.y);
-        } else {
+        const int il[4][2] = {{il0[0], il0[1]}, {il0[2], il0[3]}, {il1[0], il1[1]}, {il1[2], il1[3]}};
+        const int ih[4][2] = {{ih0[0], ih0[1]}, {ih0[2], ih0[3]}, {ih1[0], ih1[1]}, {ih1[2], ih1[3]}};
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++) {
+                int L = il[c][mi];
+                if (SIGNED) L -= __float_as_int(gs[mi]);
+                // |IL|, |IH|/16 <= 15 * 127 * 64 and their sum < 2^24: every step is exact
+                fI[c][mi] = fmaf(__int2float_rn(ih[c][mi]), 0.0625f, __int2float_rn(L));
+            }
+        }
+    } else {
+        int ia[4] = {0, 0, 0, 0}, ib[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < SETS; j++) {
+            uint2 xb = make_uint2(0u, 0u);
+            if (row_live) xb = *reinterpret_cast<const uint2*>(codes + 32 * j);
+            uint32_t l0 = q[j].x & kNibMask, l1 = q[j].y & kNibMask, l2 = q[j].z & kNibMask, l3 = q[j].w & kNibMask;
+            uint32_t h0 = (q[j].x >> 4) & kNibMask, h1 = (q[j].y >> 4) & kNibMask, h2 = (q[j].z >> 4) & kNibMask,
+                     h3 = (q[j].w >> 4) & kNibMask;
+            if (SIGNED) {
+                l0 ^= 0x08080808u, l1 ^= 0x08080808u, l2 ^= 0x08080808u, l3 ^= 0x08080808u;
+                h0 ^= 0x08080808u, h1 ^= 0x08080808u, h2 ^= 0x08080808u, h3 ^= 0x08080808u;
+            }
             mma_u8s8(ia, l0, l1, h0, h1, xb.x, xb.y);
             mma_u8s8(ib, l2, l3, h2, h3, xb.x, xb.y);
         }
-    }
-    if (SETS > 1) {
+        const int iv[4][2] = {{ia[0], ia[1]}, {ia[2], ia[3]}, {ib[0], ib[1]}, {ib[2], ib[3]}};
 #pragma unroll
-        for (int i = 0; i < 4; i++) ia[i] += ja[i], ib[i] += jb[i];
+        for (int c = 0; c < 4; c++) {
+#pragma unroll
+            for (int mi = 0; mi < 2; mi++) {
+                int I = iv[c][mi];
+                if (SIGNED) I -= __float_as_int(gs[mi]);
+                fI[c][mi] = __int2float_rn(I);  // |I| <= 15 * 127 * 32: exact
+            }
+        }
     }
-    const float4 s4 = *reinterpret_cast<const float4*>(sc + t * 4);  // scale, aux of rows 2t and 2t+1
     const float2 wd01 = __half22float2(*reinterpret_cast<const __half2*>(&wd.x));
     const float2 wd23 = __half22float2(*reinterpret_cast<const __half2*>(&wd.y));
     const float wdf[4] = {wd01.x, wd01.y, wd23.x, wd23.y};
-    const int iv[4][2] = {{ia[0], ia[1]}, {ia[2], ia[3]}, {ib[0], ib[1]}, {ib[2], ib[3]}};
-    const float xs[2] = {s4.x, s4.z};
-    const float gs[2] = {s4.y, s4.w};
     float wmf[4] = {0.f, 0.f, 0.f, 0.f};
     if (QTYPE == 1) {
         const float2 wm01 = __half22float2(*reinterpret_cast<const __half2*>(&wm.x));
@@ -140,10 +182,7 @@ __device__ __forceinline__ void block_accumulate(const uint4 (&q)[G / 32], uint2
     for (int c = 0; c < 4; c++) {
 #pragma unroll
         for (int mi = 0; mi < 2; mi++) {
-            int I = iv[c][mi];
-            if (SIGNED) I -= __float_as_int(gs[mi]);
-            // |I| <= 15 * 127 * 128 < 2^22: the conversion is exact
-            acc[c][mi] = fmaf(__fmul_rn(wdf[c], xs[mi]), exact_i2f(I), acc[c][mi]);
+            acc[c][mi] = fmaf(__fmul_rn(wdf[c], xs[mi]), fI[c][mi], acc[c][mi]);
             if (QTYPE == 1) acc[c][mi] = fmaf(wmf[c], gs[mi], acc[c][mi]);
         }
     }

@@ -1,5 +1,6 @@
-// Single-GPU instantiations of the ring decode kernel (fc_decode_ring_impl.cuh, TP = false), and the status
+// Single-GPU instantiations of the decode kernel (fc_decode_ring_impl.cuh, TP = false), and the status
 // word its kernels use when the caller passes no workspace.
+#define Q4FC_TL_NAME q4fc_dbg_set_tl
 #include "fc_decode_ring_impl.cuh"
 
 namespace q4fc {
@@ -35,18 +36,28 @@ int* ring_status_word() {
 int launch_fc_decode_ring(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng, int64_t Kg,
                           int qtype, int G, int64_t N, float* y, int64_t ldy, unsigned flags, cudaStream_t s, void* ws,
                           size_t ws_bytes, const void* xq, const float* addend, int64_t addend_ld) {
-    RingJob job = {wq, Ng, N, y, ldy, addend, addend_ld};
-    return launch_ring_impl<false>(x, rows, K, ldx, Kg, qtype, G, &job, 1, flags, s, nullptr, ws, ws_bytes, xq);
+    const RingCall c = {x, ldx, xq, rows, K, Kg, wq, Ng, N, y, ldy, addend, addend_ld};
+    return launch_ring_impl<false>(&c, 1, qtype, G, flags, s, nullptr, ws, ws_bytes);
 }
 
 int launch_fc_decode_ring_multi(const float* x, int rows, int64_t K, int64_t ldx, int64_t Kg, int qtype, int G,
                                 const q4fc_fc_job* jobs, int njobs, unsigned flags, cudaStream_t s, void* ws,
                                 size_t ws_bytes, const void* xq) {
-    RingJob rj[kMaxJobs];
+    RingCall c[kMaxJobs];
     for (int i = 0; i < njobs; i++)
-        rj[i] = {static_cast<const uint8_t*>(jobs[i].wq), jobs[i].Ng, jobs[i].N, jobs[i].y, jobs[i].ldy, jobs[i].addend,
-                 jobs[i].ld_addend};
-    return launch_ring_impl<false>(x, rows, K, ldx, Kg, qtype, G, rj, njobs, flags, s, nullptr, ws, ws_bytes, xq);
+        c[i] = {x, ldx, xq, rows, K, Kg, static_cast<const uint8_t*>(jobs[i].wq), jobs[i].Ng, jobs[i].N, jobs[i].y,
+                jobs[i].ldy, jobs[i].addend, jobs[i].ld_addend};
+    return launch_ring_impl<false>(c, njobs, qtype, G, flags, s, nullptr, ws, ws_bytes);
+}
+
+int launch_fc_decode_ring_batch(const q4fc_fc_call* calls, int ncalls, int qtype, int G, unsigned flags,
+                                cudaStream_t s) {
+    RingCall c[kMaxJobs];
+    for (int i = 0; i < ncalls; i++)
+        c[i] = {nullptr, 0, calls[i].xq, (int)calls[i].rows, calls[i].K, calls[i].Kg,
+                static_cast<const uint8_t*>(calls[i].wq), calls[i].Ng, calls[i].N, calls[i].y, calls[i].ldy,
+                calls[i].addend, calls[i].ld_addend};
+    return launch_ring_impl<false>(c, ncalls, qtype, G, flags, s, nullptr, nullptr, 0);
 }
 
 }  // namespace q4fc

@@ -1,6 +1,7 @@
-// Multi-GPU instantiations of the ring decode kernel (fc_decode_ring_impl.cuh, TP = true): outputs leave as
+// Multi-GPU instantiations of the decode kernel (fc_decode_ring_impl.cuh, TP = true): outputs leave as
 // epoch-stamped 64-bit words stored into every rank's buffer, inputs may be such a buffer.  Also the two
 // small kernels around them: the step barrier and the unpacking of a stamped buffer.
+#define Q4FC_TL_NAME q4fc_dbg_set_tl_tp
 #include "fc_decode_ring_impl.cuh"
 
 namespace q4fc {
@@ -81,8 +82,8 @@ __global__ void tp_collect_kernel(const unsigned long long* src, int rows, int64
 int launch_fc_decode_ring_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,
                              const q4fc_tp_site* tp) {
-    RingJob job = {wq, Ng, N, nullptr, ldy, nullptr, 0};
-    return launch_ring_impl<true>(x, rows, K, ldx, Kg, qtype, G, &job, 1, flags, s, &tp, nullptr, 0, nullptr);
+    const RingCall c = {x, ldx, nullptr, rows, K, Kg, wq, Ng, N, nullptr, ldy, nullptr, 0};
+    return launch_ring_impl<true>(&c, 1, qtype, G, flags, s, &tp, nullptr, 0);
 }
 
 int launch_tp_step_begin(unsigned long long* epoch, unsigned long long* const* barrier_peer,

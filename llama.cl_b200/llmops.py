@@ -23,7 +23,7 @@ from . import _cabi
 from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, FLAG_STREAMK, Q4_0, Q4_1
 
 __all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
-           "fc_workspace", "Workspace", "fc_Q4A_multi", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize",
+           "fc_workspace", "Workspace", "fc_Q4A_multi", "FCBatch", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize",
            "QuantizedActivations"]
 
 
@@ -381,6 +381,62 @@ def fc_Q4A_multi(input, weights, Ns, *, outs=None, addends=None, workspace: Work
             Kg, q, G, jobs, len(weights), workspace.ptr if workspace is not None else None,
             workspace.nbytes if workspace is not None else 0, flags, _stream_ptr(dev)), "fc_Q4A_multi")
     return outs
+
+
+class FCBatch:
+    """A fixed batch of independent FCs that runs as ONE launch (``q4fc_fc_decode_batch``).
+
+    ``calls``: up to 16 tuples ``(xq, wei_quantized, N)`` or ``(xq, wei_quantized, N, out)`` with ``xq`` a
+    ``QuantizedActivations`` (several calls may share one) and the weights all of one block type.  The argument
+    block is built once; ``run()`` only launches, so the object is cheap to call per step and safe to capture in
+    a CUDA graph.  ``outs`` holds the outputs, each equal to ``fc_Q4A_q8`` of that call alone within the rounding
+    of the fp32 sums."""
+
+    def __init__(self, calls, *, pdl: bool = False) -> None:
+        if not 1 <= len(calls) <= 16:
+            raise RuntimeError("FCBatch: one to sixteen calls")
+        self.n = len(calls)
+        self._args = (_cabi.FcCall * self.n)()
+        self._keep = []
+        self.outs = []
+        q = G = None
+        signed = False
+        for i, call in enumerate(calls):
+            xq, w, N = call[0], call[1], int(call[2])
+            out = call[3] if len(call) > 3 else None
+            if not isinstance(xq, QuantizedActivations):
+                raise RuntimeError("FCBatch: inputs must be QuantizedActivations (quantize_activations / rmsnorm_quantize)")
+            _require_cuda(w, f"calls[{i}] weights", torch.int8, 3)
+            qi, Gi = _cabi.infer_variant(w.shape[2])
+            if q is None:
+                q, G, self.device = qi, Gi, w.device
+            elif (qi, Gi) != (q, G):
+                raise RuntimeError("FCBatch: the weight tensors differ in block type")
+            if Gi != xq.group_k or int(w.shape[1]) != xq.Kg:
+                raise RuntimeError(f"calls[{i}]: activations are group {xq.group_k} x {xq.Kg}, weights {Gi} x {w.shape[1]}")
+            if xq.signed and q != Q4_0:
+                raise RuntimeError("activations quantized with nibble_signed=True serve Q4_0 weights only")
+            signed = signed or xq.signed
+            if out is None:
+                out = torch.empty((xq.B, xq.M, N), dtype=torch.float32, device=w.device)
+            else:
+                _require_cuda(out, f"calls[{i}] out", torch.float32, 3)
+                if tuple(out.shape) != (xq.B, xq.M, N):
+                    raise RuntimeError(f"calls[{i}] out: expected shape {(xq.B, xq.M, N)}, got {tuple(out.shape)}")
+            a = self._args[i]
+            a.xq, a.rows, a.K = xq.buf.data_ptr(), xq.rows, xq.K
+            a.wq, a.Ng, a.Kg, a.N = w.data_ptr(), int(w.shape[0]), int(w.shape[1]), N
+            a.y, a.ldy = out.data_ptr(), N
+            self._keep.append((xq, w))
+            self.outs.append(out)
+        self.qtype, self.group_k = q, G
+        self.flags = (FLAG_PDL if pdl else 0) | (FLAG_NIBBLE_SIGNED if (signed and q == Q4_0) else 0)
+
+    def run(self):
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.lib().q4fc_fc_decode_batch(self._args, self.n, self.qtype, self.group_k, self.flags,
+                                                         _stream_ptr(self.device)), "fc_decode_batch")
+        return self.outs
 
 
 def fc_Q4A2(input, wei_quantized, N):
