@@ -20,9 +20,9 @@
 // the slot with one mbarrier arrival per warp, feeds mma.sync.m16n8k32 (u8 x s8 -> s32, exact) and scales per
 // K group in fp32.
 //
-// Reduction.  At the end of a stripe the warps' partial sums meet in shared memory (two buffers, handed over
-// with mbarriers so that nobody waits for the slowest warp) and warp m adds row m in warp order: fixed order,
-// no atomics, no global scratch.  With cs > 1 the CTA's sum goes over distributed shared memory into the inbox of the stripe's owner
+// Reduction.  At the end of a stripe the warps' partial sums meet in shared memory (four buffers, handed over
+// with mbarriers so that nobody waits for the slowest warp) and one warp per row -- the duty moves round the
+// warps -- adds them in warp order: fixed order, no atomics, no global scratch.  With cs > 1 the CTA's sum goes over distributed shared memory into the inbox of the stripe's owner
 // (rank = stripe mod cs), which adds the cs contributions in rank order after one cluster barrier.
 //
 // Activations.  Either quantized here (one input; a warp takes 128 consecutive k of up to four rows; codes and
@@ -52,6 +52,7 @@ namespace {
 constexpr int kRW = 16;  // consumer warps
 constexpr int kRThreads = (kRW + 1) * 32;
 constexpr int kRingMax = 10;    // most slots a ring can have
+constexpr int kPartBufs = 4;    // buffers in which the warps' partial sums of successive stripes meet
 constexpr int kMaxJobs = 16;    // weight tensors per launch
 constexpr int kMaxInputs = 16;  // distinct activation tensors per launch
 constexpr int kMaxTpJobs = 4;   // weight tensors per launch in the multi-GPU form
@@ -282,8 +283,8 @@ __global__ void __launch_bounds__(kRThreads, 1) fc_decode_ring_kernel(const __gr
     constexpr int SB = S::SB;
 
     extern __shared__ __align__(128) uint8_t smem[];
-    // [0,256): mbarriers full[kRingMax], empty[kRingMax], xbar; failure flag at 192; pfull[2] at 200, pfree[2] at 216
-    // then part [2][kRW][rows_p*32] f32 | inbox [inbox_stripes][cs][rows_p*32] f32 (cs > 1) | sc [kc_max][16] f32
+    // [0,512): mbarriers full[kRingMax], empty[kRingMax], xbar; failure flag at 192; pfull[kPartBufs] at 256,
+    // pfree[kPartBufs] at 320; then part [kPartBufs][kRW][rows_p*32] f32 | inbox [inbox_stripes][cs][rows_p*32] f32 (cs > 1) | sc [kc_max][16] f32
     //      | codes [rows_max][code_stride] | ring [depth][slot_bytes]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -299,11 +300,11 @@ __global__ void __launch_bounds__(kRThreads, 1) fc_decode_ring_kernel(const __gr
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kRingMax + s); };
     const uint32_t xbar = bar0 + 8u * (2 * kRingMax);
-    auto pfull_bar = [&](int b) { return bar0 + 200u + 8u * b; };
-    auto pfree_bar = [&](int b) { return bar0 + 216u + 8u * b; };
+    auto pfull_bar = [&](int b) { return bar0 + 256u + 8u * b; };
+    auto pfree_bar = [&](int b) { return bar0 + 320u + 8u * b; };
     volatile int* fail = reinterpret_cast<volatile int*>(smem + 192);
-    float* part = reinterpret_cast<float*>(smem + 256);
-    float* inbox = part + 2 * kRW * slot_f;
+    float* part = reinterpret_cast<float*>(smem + 512);
+    float* inbox = part + kPartBufs * kRW * slot_f;
     float* sc = inbox + (cs > 1 ? p.inbox_stripes * cs * slot_f : 0);
     uint8_t* codes = reinterpret_cast<uint8_t*>(sc + p.kc_max * 16);
     uint8_t* ring = smem + p.ring_off;
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(kRThreads, 1) fc_decode_ring_kernel(const __gr
             mbar_init(empty_bar(i), kRW);
         }
         mbar_init(xbar, 1);
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < kPartBufs; i++) {
             mbar_init(pfull_bar(i), kRW);
             mbar_init(pfree_bar(i), p.rows_max);
         }
@@ -515,12 +516,13 @@ __global__ void __launch_bounds__(kRThreads, 1) fc_decode_ring_kernel(const __gr
                 if (++cs_ == depth) cs_ = 0, fph ^= 1;
             }
             // ---- the stripe's slice is done: the warps' partial sums meet in shared memory.
-            // Two buffers take turns.  Writers do not wait for one another: a warp stores its sums, arrives on
-            // the buffer's "full" barrier and goes on to the next stripe; warp m (m < rows_max) waits for all kRW
-            // arrivals, adds row m in warp order and arrives on the "free" barrier, which a writer passes before
-            // it touches the buffer again two stripes later.
-            const int buf = li & 1;
-            const uint32_t use = (uint32_t)(li >> 1);
+            // kPartBufs buffers take turns.  Writers do not wait for one another: a warp stores its sums, arrives
+            // on the buffer's "full" barrier and goes on to the next stripe.  Row m of stripe li is added, in warp
+            // order, by warp (li * rows_max + m) mod kRW -- the adding moves round the warps, so no warp is the
+            // slow one -- which then arrives on the "free" barrier; a writer passes that barrier before it touches
+            // the buffer again kPartBufs stripes later.
+            const int buf = li % kPartBufs;
+            const uint32_t use = (uint32_t)(li / kPartBufs);
             if (use > 0) mbar_wait(pfree_bar(buf), (use - 1) & 1, fail, p.status, 0x52504652);  // 'RPFR'
             float* pw = part + (buf * kRW + warp) * slot_f;
 #pragma unroll
@@ -530,22 +532,26 @@ __global__ void __launch_bounds__(kRThreads, 1) fc_decode_ring_kernel(const __gr
                         make_float4(acc[0][mi], acc[1][mi], acc[2][mi], acc[3][mi]);
             __syncwarp();
             if (lane == 0) mbar_arrive(pfull_bar(buf));
-            if (warp < p.rows_max) {
+            const int m = ((warp - li * p.rows_max) % kRW + kRW) % kRW;  // the row this warp adds, if any
+            if (m < p.rows_max) {
                 mbar_wait(pfull_bar(buf), use & 1, fail, p.status, 0x52504655);  // 'RPFU'
-                const float* src = part + buf * kRW * slot_f + warp * 32 + lane;
-                float sum = src[0];
+                const float* src = part + buf * kRW * slot_f + m * 32 + lane;
+                float sum = 0.0f;
+                if (m < rows) {
+                    sum = src[0];
 #pragma unroll
-                for (int w = 1; w < kRW; w++) sum += src[w * slot_f];
+                    for (int w = 1; w < kRW; w++) sum += src[w * slot_f];
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(pfree_bar(buf));
-                if (warp < rows) {
+                if (m < rows) {
                     if (cs > 1) {
-                        float* dst = inbox + (((li >> p.log2cs) << p.log2cs) + j) * slot_f + warp * 32 + lane;
+                        float* dst = inbox + (((li >> p.log2cs) << p.log2cs) + j) * slot_f + m * 32 + lane;
                         const int owner = li & (cs - 1);
                         if (owner != j) dst = cluster.map_shared_rank(dst, owner);
                         *dst = sum;
                     } else {
-                        final_store(d, warp, sum);
+                        final_store(d, m, sum);
                     }
                 }
             }
@@ -818,7 +824,7 @@ int launch_ring_impl(const RingCall* calls, int ncalls, int qtype, int G, unsign
         const int r_max = (int)((ng_total + nc - 1) / nc);
         p.inbox_stripes = cs > 1 ? (r_max + cs - 1) / cs : 0;
         const size_t slot_f = (size_t)p.rows_p * 32;
-        fixed = 256 + 2 * kRW * slot_f * 4 + (size_t)p.inbox_stripes * cs * slot_f * 4 + (size_t)p.kc_max * 64 +
+        fixed = 512 + kPartBufs * kRW * slot_f * 4 + (size_t)p.inbox_stripes * cs * slot_f * 4 + (size_t)p.kc_max * 64 +
                 (size_t)rows_max * p.code_stride;
         fixed = align_up(fixed, 128);
         if (fixed + 2 * (size_t)p.slot_bytes <= (size_t)di->max_smem_optin) break;
