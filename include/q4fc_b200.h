@@ -204,6 +204,13 @@ int q4fc_fc_decode_batch(const q4fc_fc_call* calls, int ncalls, int qtype, int g
  *                        chatllama/main.py:359): the row that is normalized is x + residual, and sum_out
  *                        (may be NULL, may alias x or residual) receives that sum -- the new residual
  *                        stream.  residual and sum_out share x's row stride ldx.
+ *   q4fc_silu_mul_quant  replaces llmops.itrans(gate, "silu") + llmops.imul(up, gate) (ops/op_misc.hpp:83-138,
+ *                        chatllama/main.py:365-368) + that quantizer: the value quantized is silu(gate) * up, the
+ *                        input of the down projection; prod (fp32 [rows][ldp], may be NULL) receives it.  gate and
+ *                        up share the row stride ld.  The reference evaluates the sigmoid with a polynomial exp
+ *                        and _mm256_rcp_ps (relative error up to 3.7e-4); here it is expf and an IEEE division, so
+ *                        the products agree to about 4e-4 relative -- inside the 1e-3 / 1e-4 tolerance of fp32
+ *                        outputs, not bit for bit -- and the codes are exact given those products.
  *   q4fc_fc_decode_q8    the decode FC on such a buffer. */
 size_t q4fc_xq_bytes(int64_t rows, int64_t K, int group_k);
 int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int group_k, int want_isum, void* xq,
@@ -213,6 +220,8 @@ int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, con
 int q4fc_add_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int64_t rows, int64_t K, int64_t ldx,
                            const float* weight, float eps, float* y, int64_t ldy, int group_k, int want_isum,
                            void* xq, unsigned flags, q4fc_stream_t stream);
+int q4fc_silu_mul_quant(const float* gate, const float* up, int64_t rows, int64_t K, int64_t ld, float* prod, int64_t ldp,
+                        int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream);
 int q4fc_fc_decode_q8(const void* xq, int64_t rows, int64_t K, const void* wq, int64_t Ng, int64_t Kg, int qtype,
                       int group_k, int64_t N, float* y, int64_t ldy, unsigned flags, q4fc_stream_t stream);
 

@@ -26,6 +26,7 @@ SYMBOLS = (
     "q4fc_tp_arena_create", "q4fc_tp_arena_open", "q4fc_tp_arena_close", "q4fc_tp_arena_destroy",
     "q4fc_tp_step_begin", "q4fc_tp_collect", "q4fc_fc_decode_tp", "q4fc_tp_site_bytes",
     "q4fc_xq_bytes", "q4fc_quant_x_q8", "q4fc_rmsnorm_quant", "q4fc_add_rmsnorm_quant", "q4fc_fc_decode_q8",
+    "q4fc_silu_mul_quant",
 )
 
 
@@ -111,6 +112,7 @@ def lib() -> C.CDLL:
     L.q4fc_quant_x_q8.argtypes = [vp, i64, i64, i64, i32, i32, vp, u32, vp]
     L.q4fc_rmsnorm_quant.argtypes = [vp, i64, i64, i64, vp, f32, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_add_rmsnorm_quant.argtypes = [vp, vp, vp, i64, i64, i64, vp, f32, vp, i64, i32, i32, vp, u32, vp]
+    L.q4fc_silu_mul_quant.argtypes = [vp, vp, i64, i64, i64, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_fc_decode_q8.argtypes = [vp, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, u32, vp]
     L.q4fc_tp_site_bytes.restype = sz
     if L.q4fc_tp_site_bytes() != C.sizeof(TpSite):

@@ -205,7 +205,7 @@ int q4fc_quant_x(const float* x, int64_t rows, int64_t K, int64_t ldx, int group
 
 size_t q4fc_fc_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int group_k) {
     if (!valid_variant(qtype, group_k) || rows < 0 || K < 0 || N < 0) return 0;
-    size_t need = decode_workspace_bytes(N);
+    size_t need = decode_workspace_bytes((N + 31) / 32 * 32);
     if (rows <= kMaxDecodeRows) {  // room for the quantizing launch in front of the decode kernel
         const size_t q = decode_prequant_offset() + quant_pre_bytes(rows, K, group_k);
         if (q > need) need = q;
@@ -283,6 +283,21 @@ int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int gr
     return launch_quant_x_pre(x, (int)rows, K, ldx, group_k, want_isum != 0, reinterpret_cast<int8_t*>(base),
                               reinterpret_cast<float*>(base + align_up((size_t)(rows * Kg * group_k), 256)),
                               (flags & Q4FC_FLAG_PDL) != 0, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_silu_mul_quant(const float* gate, const float* up, int64_t rows, int64_t K, int64_t ld, float* prod, int64_t ldp,
+                        int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream) {
+    if (int rc = check_xq_args("silu_mul_quant", rows, K, group_k, xq)) return rc;
+    if (rows == 0) return Q4FC_OK;
+    if (!gate || !up || ld < K || !aligned(gate, 4) || !aligned(up, 4) || (prod && (ldp < K || !aligned(prod, 4)))) {
+        set_error("silu_mul_quant: null or misaligned gate / up / prod, or a leading dimension smaller than K");
+        return Q4FC_EINVAL;
+    }
+    const int64_t Kg = (K + group_k - 1) / group_k;
+    uint8_t* base = static_cast<uint8_t*>(xq);
+    return launch_quant_x_pre(gate, (int)rows, K, ld, group_k, want_isum != 0, reinterpret_cast<int8_t*>(base),
+                              reinterpret_cast<float*>(base + align_up((size_t)(rows * Kg * group_k), 256)),
+                              (flags & Q4FC_FLAG_PDL) != 0, static_cast<cudaStream_t>(stream), up, prod, ldp);
 }
 
 int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,

@@ -79,8 +79,10 @@ int launch_rmsnorm_quant(const float* x, const float* residual, float* sum_out, 
                          int64_t ldy, int G, bool want_isum, int8_t* codes, float* sc, bool pdl, cudaStream_t s);
 // quantizing launch in front of the decode FC for large rows x K (scratch layout: quant_x.cu)
 size_t quant_pre_bytes(int64_t rows, int64_t K, int G);
+// `up` != nullptr: quantize silu(x) * up instead of x (rows of `up` share x's stride); `prod`: optional fp32 copy
 int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, bool want_isum, int8_t* codes,
-                       float* sc, bool pdl, cudaStream_t s);
+                       float* sc, bool pdl, cudaStream_t s, const float* up = nullptr, float* prod = nullptr,
+                       int64_t ldp = 0);
 // the same kernel with outputs stored, epoch-stamped, into every rank's buffer (tp->y_peer)
 int launch_fc_decode_ring_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                                 int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,

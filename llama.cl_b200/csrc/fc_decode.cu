@@ -444,8 +444,9 @@ int launch_fc_decode(const float* x, int rows, int64_t K, int64_t ldx, const uin
                   (long long)(kWsCounterCapacity / 4 * 32));
         return Q4FC_ELIMIT;
     }
-    if (ws == nullptr || ws_bytes < decode_workspace_bytes(N)) {
-        set_error("fc_decode: workspace of %zu bytes given, %zu needed", ws_bytes, decode_workspace_bytes(N));
+    // the kernel keeps a counter per stripe of the packed tensor, also of stripes beyond N
+    if (ws == nullptr || ws_bytes < decode_workspace_bytes(Ng * 32)) {
+        set_error("fc_decode: workspace of %zu bytes given, %zu needed", ws_bytes, decode_workspace_bytes(Ng * 32));
         return Q4FC_EWORKSPACE;
     }
     DecodeParams p;
@@ -522,9 +523,14 @@ extern "C" __attribute__((visibility("default"))) int q4fc_fc_decode_noalloc(
         set_error("fc_decode_noalloc: unsupported block type (qtype=%d, group_k=%d)", qtype, group_k);
         return Q4FC_EVARIANT;
     }
-    if (rows < 0 || rows > kMaxDecodeRows || K <= 0 || N < 0 || Kg <= 0 || (K + group_k - 1) / group_k != Kg ||
-        N > Ng * 32 || ldx < K || ldy < N || (rows > 0 && N > 0 && (!x || !wq || !y))) {
-        set_error("fc_decode_noalloc: bad sizes or null pointer (rows=%lld<=8, K=%lld, Kg=%lld, N=%lld, Ng=%lld)",
+    if (rows > kMaxDecodeRows) {
+        set_error("fc_decode_noalloc: rows=%lld exceeds the %d rows the entry point takes", (long long)rows,
+                  kMaxDecodeRows);
+        return Q4FC_ELIMIT;
+    }
+    if (rows < 0 || K <= 0 || N < 0 || Kg <= 0 || (K + group_k - 1) / group_k != Kg || N > Ng * 32 || ldx < K ||
+        ldy < N || (rows > 0 && N > 0 && (!x || !wq || !y))) {
+        set_error("fc_decode_noalloc: bad sizes or null pointer (rows=%lld, K=%lld, Kg=%lld, N=%lld, Ng=%lld)",
                   (long long)rows, (long long)K, (long long)Kg, (long long)N, (long long)Ng);
         return Q4FC_EINVAL;
     }
@@ -533,13 +539,14 @@ extern "C" __attribute__((visibility("default"))) int q4fc_fc_decode_noalloc(
         set_error("fc_decode_noalloc: packed weights need 16-byte alignment, x and y 4-byte");
         return Q4FC_EALIGN;
     }
-    if (N > kStaticMaxN) {
-        set_error("fc_decode_noalloc: N=%lld exceeds the built-in scratch (N <= %lld); use q4fc_fc_decode with a "
-                  "caller-provided workspace", (long long)N, (long long)kStaticMaxN);
+    // the kernel keeps a counter per stripe of the packed tensor: the limit is on Ng, not only on N
+    if (N > kStaticMaxN || Ng > kStaticMaxN / 32) {
+        set_error("fc_decode_noalloc: N=%lld (Ng=%lld) exceeds the built-in scratch (N <= %lld); use q4fc_fc_decode "
+                  "with a caller-provided workspace", (long long)N, (long long)Ng, (long long)kStaticMaxN);
         return Q4FC_ELIMIT;
     }
     if (rows == 0 || N == 0) return Q4FC_OK;
-    const size_t need = decode_workspace_bytes(N);
+    const size_t need = decode_workspace_bytes(Ng * 32);
     if (need > kStaticScratchBytes) {
         set_error("fc_decode_noalloc: this GPU needs %zu bytes of scratch, the built-in array holds %zu", need,
                   (size_t)kStaticScratchBytes);
@@ -565,8 +572,8 @@ extern "C" __attribute__((visibility("default"))) int q4fc_fc_decode_noalloc(
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // what must start at zero: the status word and this call's stripe counters
     Q4FC_CUDA_OK(cudaMemsetAsync(scratch, 0, kWsStatusBytes, s));
-    Q4FC_CUDA_OK(cudaMemsetAsync(static_cast<unsigned char*>(scratch) + need - align_up((size_t)((N + 31) / 32) * 4, 256),
-                                 0, align_up((size_t)((N + 31) / 32) * 4, 256), s));
+    Q4FC_CUDA_OK(cudaMemsetAsync(static_cast<unsigned char*>(scratch) + need - align_up((size_t)Ng * 4, 256), 0,
+                                 align_up((size_t)Ng * 4, 256), s));
     return launch_fc_decode(x, (int)rows, K, ldx, static_cast<const uint8_t*>(wq), Ng, Kg, qtype, group_k, N, y, ldy,
                             scratch, kStaticScratchBytes, flags, s);
 }

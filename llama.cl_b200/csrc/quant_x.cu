@@ -118,11 +118,19 @@ __global__ void __launch_bounds__(kQxWarps * 32) quant_x_kernel(const float* __r
 // result does not depend on which of the two quantized the input.
 //   codes: int8 [rows][Kg*G];   sc: fp32 [Kg][16], entry 2*m = scale d of row m, entry 2*m + 1 = group sum
 //   (or, for the signed-nibble Q4_0 form, the bits of the integer 8 * sum of codes).
+//
+// With `up` given the value that is quantized is silu(x) * up -- the MLP's gate activation and the product with
+// the up projection (llmops.itrans(gate, "silu") then llmops.imul(up, gate), ops/op_misc.hpp:83-138,
+// chatllama/main.py:365-368), i.e. the input of the down projection -- and `prod`, when given, receives those
+// fp32 values.  silu(g) = g / (1 + exp(-g)) with expf and an IEEE division; the reference evaluates exp by a
+// degree-5 polynomial and the reciprocal by _mm256_rcp_ps (relative error up to 3.7e-4), so the products agree
+// with it to about 4e-4 relative, inside the 1e-3 / 1e-4 output tolerance, not bit for bit.
 template <int G>
 __global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restrict__ x, int rows, int64_t K,
                                                           int64_t ldx, int64_t Kg, int vec_ok, int want_isum,
                                                           int early_release, int8_t* __restrict__ codes,
-                                                          float* __restrict__ sc) {
+                                                          float* __restrict__ sc, const float* __restrict__ up,
+                                                          float* __restrict__ prod, int64_t ldp) {
     constexpr int SEG = G / 4;
     constexpr int GPC = 128 / G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -151,6 +159,28 @@ __global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restric
 #pragma unroll
         for (int j = 0; j < 4; j++)
             if (k + j < K) v[j] = __ldcg(src + j);
+    }
+    if (up != nullptr) {
+        float u[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* usrc = up + m * ldx + k;
+        if (vec_ok && k + 4 <= K) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(usrc));
+            u[0] = a.x, u[1] = a.y, u[2] = a.z, u[3] = a.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (k + j < K) u[j] = __ldcg(usrc + j);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float sg = __fdiv_rn(v[j], __fadd_rn(1.0f, expf(-v[j])));
+            v[j] = __fmul_rn(u[j], sg);
+        }
+        if (prod != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (k + j < K) prod[m * ldp + k + j] = v[j];
+        }
     }
     float amax = 0.0f, fsum = 0.0f;
 #pragma unroll
@@ -209,11 +239,12 @@ size_t quant_pre_bytes(int64_t rows, int64_t K, int G) {
 }
 
 int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, bool want_isum, int8_t* codes,
-                       float* sc, bool pdl, cudaStream_t s) {
+                       float* sc, bool pdl, cudaStream_t s, const float* up, float* prod, int64_t ldp) {
     const int64_t Kg = (K + G - 1) / G;
     const int64_t chunks = (Kg * G + 127) / 128;
     const int64_t grid = (chunks * rows + 3) / 4;
-    const int vec_ok = (K % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const int vec_ok = (K % 4 == 0) && (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(up) & 15) == 0);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(128);
@@ -225,10 +256,10 @@ int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, 
     cfg.numAttrs = pdl ? 1 : 0;
     if (G == 32)
         Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_kernel<32>, x, rows, K, ldx, Kg, vec_ok, (int)want_isum,
-                                        (int)pdl, codes, sc));
+                                        (int)pdl, codes, sc, up, prod, ldp));
     else
         Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_kernel<128>, x, rows, K, ldx, Kg, vec_ok, (int)want_isum,
-                                        (int)pdl, codes, sc));
+                                        (int)pdl, codes, sc, up, prod, ldp));
     return Q4FC_OK;
 }
 

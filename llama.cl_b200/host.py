@@ -10,7 +10,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from . import llmops
+from . import _cabi, llmops
 
 
 class HostFC:
@@ -153,3 +153,111 @@ class HostFCGroup:
         if sync:
             self.stream.synchronize()
         return [h._y_host[:, :M] for h, M in zip(self.members, Ms)]
+
+
+class HostFCBatch:
+    """A fixed batch of independent host-buffer FCs with ONE copy each way per step: ``ys = batch(xs)``.
+
+    ``members``: tuples ``(wq, N, rows)`` -- packed weights resident on the GPU, output width, rows of that call's
+    input.  All inputs live back to back in one pinned host block and one device block, all outputs likewise, so
+    a step is: one host-to-device copy, the quantizers, the FCs (grouped into ``q4fc_fc_decode_batch`` launches
+    by row count), one device-to-host copy -- captured once as a CUDA graph and replayed.  ``x_staging(i)`` is
+    the pinned view ``[1, rows, K]`` of input i: writing activations straight into it saves the host-side copy.
+    Returns the pinned output views ``[1, rows, N]``, valid after ``sync`` (default: waited for here)."""
+
+    def __init__(self, members, *, graph: bool = True) -> None:
+        self.members = [(wq, int(N), int(rows)) for wq, N, rows in members]
+        if not self.members:
+            raise RuntimeError("HostFCBatch: no members")
+        dev = self.members[0][0].device
+        self.device = dev
+        self.stream = torch.cuda.Stream(dev)
+        self.side = torch.cuda.Stream(dev)
+        shapes = []
+        for wq, N, rows in self.members:
+            q, G = _cabi.infer_variant(wq.shape[2])
+            shapes.append((rows, int(wq.shape[1]) * G, N, G))
+        self._shapes = shapes
+        nx = sum(r * K for r, K, _, _ in shapes)
+        ny = sum(r * N for r, _, N, _ in shapes)
+        self._x_host = torch.empty(nx, dtype=torch.float32).pin_memory()
+        self._y_host = torch.empty(ny, dtype=torch.float32).pin_memory()
+        self._x_dev = torch.empty(nx, dtype=torch.float32, device=dev)
+        self._y_dev = torch.empty(ny, dtype=torch.float32, device=dev)
+        self._xs_host, self._ys_host, xs_dev, ys_dev = [], [], [], []
+        ox = oy = 0
+        for r, K, N, _ in shapes:
+            self._xs_host.append(self._x_host[ox: ox + r * K].view(1, r, K))
+            xs_dev.append(self._x_dev[ox: ox + r * K].view(1, r, K))
+            self._ys_host.append(self._y_host[oy: oy + r * N].view(1, r, N))
+            ys_dev.append(self._y_dev[oy: oy + r * N].view(1, r, N))
+            ox, oy = ox + r * K, oy + r * N
+        self._xs_dev = xs_dev
+        self._xq = [llmops.QuantizedActivations(1, r, K, G, False, dev) for r, K, _, G in shapes]
+        # one launch per row count: calls of one launch then share the size of their code buffers
+        by_rows: dict = {}
+        for i, (r, _, _, _) in enumerate(shapes):
+            by_rows.setdefault(r, []).append(i)
+        self._groups = [idx for _, idx in sorted(by_rows.items())]
+        self._batches = []
+        for idx in self._groups:
+            for j in range(0, len(idx), 16):
+                part = idx[j: j + 16]
+                self._batches.append((part, llmops.FCBatch(
+                    [(self._xq[i], self.members[i][0], self.members[i][1], ys_dev[i]) for i in part], pdl=True)))
+        self.use_graph = bool(graph)
+        self._graph = None
+
+    def x_staging(self, i: int) -> torch.Tensor:
+        return self._xs_host[i]
+
+    def _enqueue(self) -> None:
+        cur = torch.cuda.current_stream(self.device)
+        self._x_dev.copy_(self._x_host, non_blocking=True)
+        # quantizers on a side branch, group by group, so that all but the first group's hide behind the FCs
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        self.side.wait_event(ready)
+        done = []
+        with torch.cuda.stream(self.side):
+            for part, _ in self._batches:
+                for i in part:
+                    llmops.quantize_activations(self._xs_dev[i], self._shapes[i][3], out=self._xq[i])
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                done.append(ev)
+        for (part, fb), ev in zip(self._batches, done):
+            cur.wait_event(ev)
+            fb.run()
+        self._y_host.copy_(self._y_dev, non_blocking=True)
+
+    def __call__(self, xs=None, sync: bool = True):
+        if xs is not None:
+            if len(xs) != len(self.members):
+                raise RuntimeError(f"HostFCBatch: {len(xs)} inputs for {len(self.members)} members")
+            for x, stage in zip(xs, self._xs_host):
+                if tuple(x.shape) != tuple(stage.shape):
+                    raise RuntimeError(f"HostFCBatch: input {tuple(x.shape)} where {tuple(stage.shape)} is expected")
+                if x.data_ptr() != stage.data_ptr():
+                    stage.copy_(x)
+        with torch.cuda.stream(self.stream):
+            if not self.use_graph:
+                self._enqueue()
+            else:
+                if self._graph is None:
+                    self._enqueue()  # eager once: lazy look-ups and kernel attributes happen outside the capture
+                    torch.cuda.synchronize(self.device)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        self._enqueue()
+                    self._graph = g
+                self._graph.replay()
+        if sync:
+            self.stream.synchronize()
+        return self._ys_host
+
+    def h2d_bytes(self) -> int:
+        return self._x_host.numel() * 4
+
+    def d2h_bytes(self) -> int:
+        return self._y_host.numel() * 4

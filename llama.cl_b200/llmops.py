@@ -23,7 +23,7 @@ from . import _cabi
 from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, FLAG_STREAMK, Q4_0, Q4_1
 
 __all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
-           "fc_workspace", "Workspace", "fc_Q4A_multi", "FCBatch", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize",
+           "fc_workspace", "Workspace", "fc_Q4A_multi", "FCBatch", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize", "silu_mul_quantize",
            "QuantizedActivations"]
 
 
@@ -291,6 +291,34 @@ def rmsnorm_quantize(input: torch.Tensor, weight: torch.Tensor, eps: float, grou
             sum_out.data_ptr() if sum_out is not None else None, B * M, K, K, weight.data_ptr(), float(eps),
             normalized.data_ptr() if normalized is not None else None, K, group_k, int(nibble_signed),
             xq.buf.data_ptr(), FLAG_PDL if pdl else 0, _stream_ptr(input.device)), "rmsnorm_quantize")
+    return xq
+
+
+def silu_mul_quantize(gate: torch.Tensor, up: torch.Tensor, group_k: int, *, product: torch.Tensor | None = None,
+                      nibble_signed: bool = False, pdl: bool = False,
+                      out: QuantizedActivations | None = None) -> QuantizedActivations:
+    """``llmops.itrans(gate, "silu")``, ``llmops.imul(up, gate)`` (ops/op_misc.hpp:83-138, chatllama/main.py:365-368)
+    and the quantizer of the down projection behind them in one kernel.
+
+    ``gate``, ``up`` fp32 ``[B, M, K]`` are left untouched; ``product`` (same shape), when given, receives
+    ``silu(gate) * up``.  The reference's sigmoid uses an approximate reciprocal, so the products agree with
+    it to about 4e-4 relative (not bit for bit); the codes are exact given the products."""
+    _require_cuda(gate, "gate", torch.float32, 3)
+    _require_cuda(up, "up", torch.float32, 3)
+    if up.shape != gate.shape:
+        raise RuntimeError("up: shape differs from gate")
+    B, M, K = gate.shape
+    _check_rows(B * M)
+    if product is not None:
+        _require_cuda(product, "product", torch.float32, 3)
+        if product.shape != gate.shape:
+            raise RuntimeError("product: shape differs from gate")
+    xq = out if out is not None else QuantizedActivations(B, M, K, group_k, nibble_signed, gate.device)
+    with torch.cuda.device(gate.device):
+        _cabi.check(_cabi.lib().q4fc_silu_mul_quant(
+            gate.data_ptr(), up.data_ptr(), B * M, K, K, product.data_ptr() if product is not None else None, K,
+            group_k, int(nibble_signed), xq.buf.data_ptr(), FLAG_PDL if pdl else 0, _stream_ptr(gate.device)),
+            "silu_mul_quantize")
     return xq
 
 

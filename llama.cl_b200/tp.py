@@ -4,11 +4,16 @@ Every 32-column stripe ``nb`` of the packed tensor ``[Ng, Kg, BS]`` is
 independent (own weights, own outputs) and the tensor is contiguous along
 ``Ng``, so a rank's shard is a contiguous byte slice of the reference's packed
 tensor and packing shards rank by rank gives the same bytes as packing the
-whole matrix.  Activations are replicated; each rank computes
-``y[:, n0:n1]`` with the ordinary FC kernel and the slices are joined with one
-all-gather (NCCL over NVLink on GPUs; any ``torch.distributed`` backend works,
-which is how the host logic is tested on CPU).  No summation order changes, so
-the joined output is bit-equal to the single-GPU output.
+whole matrix.  Activations are replicated; each rank computes ``y[:, n0:n1]``.
+Two ways to join the slices:
+
+``TPLinearQ4``       one all-gather after the FC (NCCL over NVLink on GPUs; any ``torch.distributed`` backend
+                     works, which is how the host logic is tested on CPU).
+``FusedTPLinearQ4``  the FC kernel itself stores its columns, stamped with a step counter, into every rank's
+                     output buffer over NVLink (``q4fc_fc_decode_tp``); consumers wait word by word for the
+                     current stamp.  No collective call, no extra launch.  After a synchronization the caller
+                     checks ``TPArena.check()``: a bounded wait on another rank that ran out leaves a status
+                     word set and the results of that step invalid.
 
 The reference has no multi-device code; this module has no counterpart there.
 """
@@ -405,4 +410,5 @@ class HostFusedFC:
                 self._enqueue(M)
         if sync:
             self.stream.synchronize()
+            self.layer.arena.check()  # a bounded wait on another rank that ran out makes the result invalid
         return self._y_host[:, :M]

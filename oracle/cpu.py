@@ -63,6 +63,7 @@ class _Restated:
             lib.oracle_quant_x.argtypes = [fp, i64, i64, i32, f32, i8p, fp, fp]
             lib.oracle_fc.argtypes = [fp, i64, i64, u8p, i64, i64, i32, i32, i64, i32, fp, i64]
             lib.oracle_rmsnorm.argtypes = [fp, i64, i64, fp, f32]
+            lib.oracle_silu_mul.argtypes = [fp, fp, i64, fp]
             lib.oracle_f32_to_f16.argtypes = [f32]
             lib.oracle_f32_to_f16.restype = C.c_uint16
             lib.oracle_f16_to_f32.argtypes = [C.c_uint16]
@@ -131,6 +132,16 @@ class _Restated:
         if rc:
             raise RuntimeError(f"oracle_rmsnorm failed ({rc})")
         return y
+
+    def silu_mul(self, gate, up) -> np.ndarray:
+        """up * silu(gate) as the reference's itrans("silu") + imul compute it (ops/op_misc.hpp:83-138), with an
+        exact reciprocal in place of its approximate one."""
+        g, u = _f32(gate), _f32(up)
+        out = np.empty_like(g)
+        rc = self.lib.oracle_silu_mul(_p(g, C.c_float), _p(u, C.c_float), g.size, _p(out, C.c_float))
+        if rc:
+            raise RuntimeError(f"oracle_silu_mul failed ({rc})")
+        return out
 
     def f16_bits(self, v: float) -> int:
         return int(self.lib.oracle_f32_to_f16(v))

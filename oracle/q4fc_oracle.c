@@ -359,6 +359,42 @@ int oracle_rmsnorm(float* x, int64_t rows, int64_t K, const float* w, float eps)
     return 0;
 }
 
+/* exp_ps_avx2 (ops/utils.hpp:293-371) for one value: clamp to [log(FLT_MIN), log(FLT_MAX)], n = floor(x*log2e + 0.5),
+ * r = x - n*ln2 (one fused multiply-add), degree-5 polynomial in r (Horner, fused), times 2^(n-1), times 2;
+ * inputs below log(FLT_MIN) give 0. */
+static float ref_expf(float x) {
+    union { uint32_t u; float f; } lo = {0xc2aeac50u}, hi = {0x42b17218u}, log2e = {0x3fb8aa3bu}, ln2 = {0x3f317218u},
+        p1 = {0x3f7ffffbu}, p2 = {0x3efffee3u}, p3 = {0x3e2aad40u}, p4 = {0x3d2b9d0du}, p5 = {0x3c07cfceu}, two_n;
+    const int zero = x < lo.f;
+    if (x > hi.f) x = hi.f;
+    if (x < lo.f) x = lo.f;
+    float fx = floorf(x * log2e.f + 0.5f);
+    const float r = fmaf(-fx, ln2.f, x);
+    fx -= 1.0f;
+    two_n.u = (uint32_t)((int32_t)lrintf(fx) + 127) << 23;
+    float y = p5.f;
+    y = fmaf(y, r, p4.f);
+    y = fmaf(y, r, p3.f);
+    y = fmaf(y, r, p2.f);
+    y = fmaf(y, r, p1.f);
+    y = fmaf(y, r, 1.0f);
+    y = y * (zero ? 0.0f : two_n.f);
+    return y * 2.0f;
+}
+
+/* llmops.itrans(gate, "silu") then llmops.imul(up, gate) (ops/op_misc.hpp:83-138, chatllama/main.py:365-368):
+ * out = up * (gate * sigmoid(gate)), sigmoid(v) = rcp(1 + exp(-v)).  The reference's rcp is _mm256_rcp_ps, a
+ * hardware approximation (relative error <= 1.5 * 2^-12) that plain C cannot reproduce bit for bit; this
+ * restatement divides exactly, so it agrees with the compiled reference to about 4e-4 relative -- the golden
+ * rows of tests/golden/silu_mul_ref.npz pin it to that. */
+int oracle_silu_mul(const float* gate, const float* up, int64_t n, float* out) {
+    for (int64_t i = 0; i < n; i++) {
+        const float sig = 1.0f / (1.0f + ref_expf(0.0f - gate[i]));
+        out[i] = up[i] * (gate[i] * sig);
+    }
+    return 0;
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

@@ -1,4 +1,5 @@
-"""N-split tensor parallelism on real GPUs: two NCCL ranks, outputs bit-equal to the single-GPU FC."""
+"""N-split tensor parallelism on real GPUs: NCCL ranks (two, and -- for boxes with one GPU -- a world of one, where
+the peer stores go to the rank's own buffers), outputs checked against the CPU oracle and the single-GPU FC."""
 import os
 import sys
 import tempfile
@@ -71,6 +72,9 @@ def _fused_worker(rank, world, initfile, result_q):
     try:
         import llama_cl_b200 as pkg
         from llama_cl_b200 import tp
+        from oracle import build_oracle, cpu
+
+        build_oracle.build_restatement()
 
         def expect(cond, what):
             if not bool(cond):
@@ -102,10 +106,16 @@ def _fused_worker(rank, world, initfile, result_q):
             last = lay["last"](down)
             return {n: o.tensor() for n, o in (("q", q), ("k", k), ("up", up), ("down", down), ("last", last))}
 
-        def verify(x, outs, tag):
+        full_np = {n: w.cpu().numpy() for n, w in full.items()}
+
+        def verify(x, outs, tag, with_oracle=False):
             got = {n: o.clone() for n, o in outs.items()}
             ins = {"q": x, "k": x, "up": got["q"], "down": got["up"], "last": got["down"]}
             for name, (N, K, _, _) in specs.items():
+                if with_oracle:
+                    # the CPU restatement of the reference's fc_Q4A on the same inputs
+                    ref = torch.from_numpy(cpu.restated.fc(ins[name].cpu().numpy(), full_np[name], N)).to(dev)
+                    expect(torch.allclose(got[name], ref, rtol=1e-3, atol=1e-4), f"{tag} {name}: differs from the oracle")
                 want = pkg.llmops.fc_Q4A(ins[name].contiguous(), full[name], N)
                 expect(got[name].shape == want.shape, f"{tag} {name}: shape {tuple(got[name].shape)}")
                 expect(torch.allclose(got[name], want, rtol=1e-3, atol=1e-4), f"{tag} {name}: differs from one GPU")
@@ -120,7 +130,7 @@ def _fused_worker(rank, world, initfile, result_q):
                 x = torch.randn(1, rows, H, generator=g).to(dev)
                 outs = chain(x)
                 torch.cuda.synchronize()
-                verify(x, outs, f"rows={rows} step={step}")
+                verify(x, outs, f"rows={rows} step={step}", with_oracle=(step == 0))
 
         # the same chain replayed as a CUDA graph: the epoch lives on the device, so replays advance it
         xg = torch.zeros(1, 1, H, device=dev)
@@ -137,7 +147,7 @@ def _fused_worker(rank, world, initfile, result_q):
             xg.copy_(torch.randn(1, 1, H, generator=g))
             graph.replay()
             torch.cuda.synchronize()
-            verify(xg, outs_g, f"graph step={step}")
+            verify(xg, outs_g, f"graph step={step}", with_oracle=(step == 2))
         expect(arena.status() == 0, f"status {arena.status():#x} after the chains")
 
         # a wait that nothing satisfies gives up after its limit, flags it, and leaves the context usable
@@ -211,3 +221,20 @@ def test_tp_two_gpus_fused_peer_stores(lib_built):
             if p.exitcode is None:
                 p.kill()  # exactly the processes started above
     assert results == [(0, []), (1, [])], results
+
+
+def test_tp_fused_world_of_one(lib_built):
+    """The whole fused N-split path on ONE GPU: arena, step barrier, stamped peer stores (to the rank's own
+    buffers), stamped inputs, unpacking kernel, graph replay, and a bounded wait that runs out and recovers --
+    each FC checked against the CPU oracle."""
+    assert torch.cuda.is_available()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        p = ctx.Process(target=_fused_worker, args=(0, 1, os.path.join(d, "init"), q))
+        p.start()
+        results = [q.get(timeout=280)]
+        p.join(60)
+        if p.exitcode is None:
+            p.kill()  # exactly the process started above
+    assert results == [(0, [])], results

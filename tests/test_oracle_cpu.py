@@ -148,3 +148,15 @@ def test_rmsnorm_restatement_matches_the_reference_rows():
         assert np.array_equal(got, f[f"y{i}"]), i
     with pytest.raises(RuntimeError):
         cpu.restated.rmsnorm(np.zeros((1, 1, 12), np.float32), np.ones(12, np.float32), 1e-5)  # K % 8 != 0
+
+
+def test_silu_mul_restatement_against_reference_rows(oracle, golden_dir):
+    """up * silu(gate) as restated (polynomial exp of ops/utils.hpp:293-371, exact reciprocal) against the rows the
+    reference's own module returned: its _mm256_rcp_ps is approximate, so the match is to tolerance, not bits."""
+    d = np.load(os.path.join(golden_dir, "silu_mul_ref.npz"))
+    for i in range(int(d["cases"])):
+        got = oracle.restated.silu_mul(d[f"gate{i}"], d[f"up{i}"])
+        ref = d[f"prod{i}"]
+        assert np.allclose(got, ref, rtol=1e-3, atol=1e-4), (i, np.abs(got - ref).max())
+        big = np.abs(ref) > 1e-3
+        assert (np.abs(got - ref)[big] / np.abs(ref)[big]).max() < 5e-4

@@ -38,7 +38,7 @@ def test_noalloc_matches_workspace_entry_point(lib_built, qname, q, G):
 
     L = pkg._cabi.lib()
     g = torch.Generator().manual_seed(123)
-    for (N, K, rows) in [(4096, 4096, 1), (11008, 4096, 8), (96, 512, 3)]:
+    for (N, K, rows) in [(4096, 4096, 1), (11008, 4096, 8), (96, 512, 3), (72, 256, 2)]:
         W = (torch.randn(N, K, generator=g) * 0.02).cuda()
         wq = pkg.llmops.offline_FC_quant_Q4A(W, qtype=qname, group_k=G)
         ws = torch.zeros(int(L.q4fc_fc_workspace_bytes(rows, K, N, q, G)), dtype=torch.uint8, device="cuda")
@@ -62,4 +62,7 @@ def test_noalloc_rejects_sizes_beyond_the_scratch(lib_built):
     N = 262144 + 32
     rc = L.q4fc_fc_decode_noalloc(16, 1, 128, 128, 16, N // 32, 1, 1, 128, N, 16, N, 0, None)
     assert rc == 7 and b"exceeds the built-in scratch" in L.q4fc_last_error()
-    assert L.q4fc_fc_decode_noalloc(16, 9, 128, 128, 16, 1, 1, 1, 128, 32, 16, 32, 0, None) == 1
+    # more rows than the entry point takes: a stated limit, reported as such
+    assert L.q4fc_fc_decode_noalloc(16, 9, 128, 128, 16, 1, 1, 1, 128, 32, 16, 32, 0, None) == 7
+    # a packed tensor with more stripes than the scratch has counters for, even though N itself is small
+    assert L.q4fc_fc_decode_noalloc(16, 1, 128, 128, 16, 8193, 1, 1, 128, 64, 16, 64, 0, None) == 7
