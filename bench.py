@@ -12,25 +12,29 @@ per step, four times the L2), so no call finds its weights in cache.  Weights
 ~ N(0, 0.02), activations ~ N(0, 1), seeded, synthetic.
 
 value  packed weight GB/s (packed bytes / time, 1 GB = 1e9 B: the reference's
-       own "Bound: GB/s" figure of ops/perf_ops.py:243-245), inputs resident
-       in HBM, the 16 calls of a step replayed as one CUDA graph.  The calls
-       are independent, so the graph runs them on --lanes parallel branches
-       (default 4); the roofline figure is taken from a second timed pass with
-       the same launches strictly one after the other.
-e2e    the same metric through the host-buffer API (HostFC / HostFCGroup):
-       activations copied from pinned host memory, results copied back to
-       pinned host memory, every call, the step's calls submitted together.
+       own "Bound: GB/s" figure of ops/perf_ops.py:243-245), inputs (fp32
+       activations, packed weights) resident in HBM.  The 16 calls of a step
+       are independent, so a step quantizes the 16 inputs and runs the FCs as
+       four launches of q4fc_fc_decode_batch (one per row count), replayed as
+       one CUDA graph.  The timed region runs every step `inner` times so that
+       it lasts about half a second; ms_per_step is per single step.
+roofline  the dominant kernel (fc_decode_ring_kernel) alone: a second timed
+       pass over the same FC launches with the inputs already quantized;
+       achieved = algorithmic bytes per launch / average launch duration.
+       `per_call` lists every (shape, M) as a single call, in order, as
+       ops/perf_ops.py:190-245 measures it (rotating distinct weights).
+e2e    the same sweep through host.HostFCBatch: host buffers in and out, one
+       pinned block and one copy each way per step, inside the timed region.
 
 With --gpus N > 1 every FC weight is split along N over the ranks (strong
 scaling: the job is the same sweep, each rank streams 1/N of every weight).
 --tp fused (default): the FC kernel stores its columns, stamped with the
-step number, into every rank's output buffer over NVLink; consumers wait
-word by word for the current stamp.
---tp nccl: the slices are joined by an NCCL all-gather after every FC.
+step number, into every rank's output buffer over NVLink.  The same sweep
+joined by an NCCL all-gather after every FC is timed beside it (`tp_nccl`).
 
 --impl reference times the reference's own CPU FC (compiled from its sources
 into oracle/_ref when that was possible, else the C restatement in oracle/)
-on the host cores, on the same sweep.
+on all host cores, on the same sweep.
 """
 from __future__ import annotations
 
@@ -49,11 +53,12 @@ SHAPES = [(4096, 4096), (4096, 11008), (11008, 4096), (4096, 32000)]  # (K, N)
 MS = [1, 2, 4, 8]
 QTYPE, GROUP_K = 1, 128
 BS = 16 * GROUP_K + 128
-# DRAM bytes per decode launch of this sweep from one ncu capture (3,561,665,024 B over 113 launches), against
-# 31.89 MB of algorithmic bytes per launch
-DECODE_TRAFFIC_PER_LAUNCH = 31.52e6
+# DRAM bytes per launch of the dominant kernel from one ncu capture of the four-launch step (profiles/), against
+# the algorithmic bytes of those launches
+DECODE_TRAFFIC_RATIO = 0.99
 METRIC = "Q4_1 FC decode weight GB/s"
 UNIT = "GB/s"
+TIMED_REGION_S = 0.5
 
 
 def packed_bytes(K: int, N: int) -> int:
@@ -135,12 +140,17 @@ class ClockSampler:
             self._thread.join()
         s = sorted(self.samples)
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(s)}
+                "reasons": sorted(self.reasons), "samples": len(s),
+                "note": "sampled by NVML every 4 ms inside the timed region"}
 
 
 # ------------------------------------------------------------- reference arm
 def host_cpu_info() -> tuple[str, int]:
-    model, n = "unknown", os.cpu_count() or 1
+    model = "unknown"
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
     try:
         with open("/proc/cpuinfo") as f:
             for line in f:
@@ -153,7 +163,8 @@ def host_cpu_info() -> tuple[str, int]:
 
 
 def cpu_sweep_setup(shapes, ms):
-    """Seeded inputs and packed weights for the CPU legs, packed by the CPU checker itself."""
+    """Seeded inputs and packed weights for the CPU legs, packed by the CPU checker itself; the OpenMP team is set
+    to the cores this process may run on (a launcher may have exported OMP_NUM_THREADS=1 for its children)."""
     import numpy as np
 
     from oracle import build_oracle, cpu
@@ -161,6 +172,7 @@ def cpu_sweep_setup(shapes, ms):
     build_oracle.build_restatement()
     use_ref = cpu.have_compiled_reference(QTYPE, GROUP_K)
     impl = cpu.compiled_reference(QTYPE, GROUP_K) if use_ref else None
+    _, ncpu = host_cpu_info()
     rng = np.random.default_rng(0)
     work = []
     for K, N in shapes:
@@ -171,8 +183,9 @@ def cpu_sweep_setup(shapes, ms):
             x = rng.standard_normal((1, M, K), dtype=np.float32)
             work.append((x, wq.copy(), N))  # a clone per M, as ops/perf_ops.py:234-236 rotates clones
     if use_ref:
+        cores = impl.set_threads(ncpu)
         run = lambda x, wq, N: impl.fc(x, wq, N)  # noqa: E731
-        kind, cores = "reference", impl.threads()
+        kind = "reference"
     else:
         run = lambda x, wq, N: cpu.restated.fc(x, wq, N)  # noqa: E731
         kind, cores = "port", cpu.restated.threads()
@@ -196,9 +209,10 @@ def reference_arm(args) -> None:
     if rank != 0:
         return
     work, run, kind, cores = cpu_sweep_setup(SHAPES, MS)
-    warm = max(1, min(args.warmup, 3))
+    warm = max(args.warmup, 3)
     # bound the run to about a minute of CPU work
     t_probe = time_cpu_sweep(work, run, 1, 1)
+    warm = max(1, min(warm, int(10.0 / max(t_probe, 1e-6))))
     steps = max(1, min(args.steps, int(60.0 / max(t_probe, 1e-6))))
     sec = time_cpu_sweep(work, run, steps, warm)
     value = STEP_WEIGHT_BYTES / sec / 1e9
@@ -209,21 +223,23 @@ def reference_arm(args) -> None:
         "vs_baseline": None, "dtype": "int8xuint4->int32, fp32 scaling", "data": "synthetic", "config": CONFIG,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
                          "sample": f"the whole 16-call sweep, {steps} timed passes; host CPU {model}, "
-                                   f"{ncpu} logical CPUs, {cores} OpenMP threads"},
+                                   f"{ncpu} usable logical CPUs, {cores} OpenMP threads"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     _emit(json.dumps(line))
 
 
 # ------------------------------------------------------------------- our arm
-def our_arm(args) -> None:
+def our_arm(args) -> int:
     import torch
     import torch.distributed as dist
 
     import llama_cl_b200 as pkg
     from llama_cl_b200 import tp
-    from llama_cl_b200.host import HostFC
+    from llama_cl_b200.host import HostFCBatch
+    from llama_cl_b200.stack import DecodeFCStack
 
+    ops = pkg.llmops
     sections = set(args.sections.split(","))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -237,12 +253,54 @@ def our_arm(args) -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     pkg._cabi.lib()
+    peak, peak_kind = load_peaks()
+    warmup = max(args.warmup, 3)
+
+    def barrier() -> None:
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if not distributed:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def capture(fn):
+        """Two eager runs (kernel attributes, lazy look-ups), then one CUDA graph of fn."""
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        torch.cuda.synchronize()
+        return g.replay
+
+    def timed(run, n: int, warm: int = 3, sample_clocks: bool = False):
+        """(ms per run, clocks) over n runs on the device, max over ranks; every rank makes the same n runs."""
+        for _ in range(warm):
+            run()
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        barrier()
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            run()
+        e1.record()
+        barrier()
+        clocks = sampler.stop() if sampler else None
+        return max_over_ranks(e0.elapsed_time(e1)) / n, clocks
 
     # ---- how the ranks' column slices meet
     arena, tp_mode, tp_note = None, ("none" if not distributed else args.tp), None
     if distributed and tp_mode == "fused":
         try:
-            arena = tp.TPArena(128 << 20, dev)
+            arena = tp.TPArena(160 << 20, dev)
         except Exception as e:  # no peer mapping on this box: the collective-library form still works
             tp_note = f"peer-mapped arena unavailable ({e}); joined by NCCL all-gather instead"
             print(f"[bench] {tp_note}", file=sys.stderr)
@@ -252,357 +310,307 @@ def our_arm(args) -> None:
         if int(flag.item()) == 0 and tp_mode == "fused":
             tp_mode, tp_note = "nccl", "another rank could not map the arena; joined by NCCL all-gather instead"
     fused = tp_mode == "fused"
-    # a schedule is a set of FCs that always run together: the sweep is one, the token pass another,
-    # and each call of the host-buffer leg stands alone
-    sweep_sched = tp.TPSchedule(arena) if fused else None
+    status_words: dict = {}
 
-    def make_layer(sched, wq_, N_, max_rows=8, prequant=False):
-        if fused:
-            return tp.FusedTPLinearQ4(sched, wq_, N_, max_rows=max_rows, pdl=True, prequant=prequant)
-        return tp.TPLinearQ4(wq_, N_, pdl=True, workspace=ws, path="decode")
+    def section_status(name: str) -> None:
+        """Reads and clears the status word of the peer-store path after a section: non-zero means a bounded wait on
+        another rank ran out, and everything timed in that section is void."""
+        if not fused:
+            return
+        st = arena.status()
+        t = torch.tensor([st], device=dev, dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        status_words[name] = int(t.item())
+        arena.tensor(arena.STATUS, (1,), torch.int32).zero_()
+        torch.cuda.synchronize()
 
     # ---- inputs: one packed weight per (shape, M); with TP each rank packs only its rows
-    ws = pkg.llmops.fc_workspace(8, 11008, 32000, QTYPE, GROUP_K, dev)
     gen = torch.Generator(device=dev)
     calls = []
+    sweep_sched = tp.TPSchedule(arena) if fused else None
     for si, (K, N) in enumerate(SHAPES):
         for M in MS:
             gen.manual_seed(1000 * si + M)
             n0, n1 = tp.shard_rows(N, world, rank) if distributed else (0, N)
             W = torch.randn((N, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
-            wq = pkg.llmops.offline_FC_quant_Q4A(W[n0:n1].contiguous(), qtype="q4_1", group_k=GROUP_K)
+            wq = ops.offline_FC_quant_Q4A(W[n0:n1].contiguous(), qtype="q4_1", group_k=GROUP_K)
             del W
             x = torch.randn((1, M, K), generator=gen, device=dev, dtype=torch.float32)
-            layer = make_layer(sweep_sched, wq, N, prequant=args.lanes > 1) if distributed else None
-            calls.append({"x": x, "wq": wq, "N": N, "n_local": n1 - n0, "M": M, "K": K, "layer": layer,
-                          "y_full": torch.empty((1, M, N), device=dev, dtype=torch.float32) if fused else None,
-                          "y": torch.empty((1, M, n1 - n0), device=dev, dtype=torch.float32)})
-    torch.cuda.synchronize()
-
-    # The 16 calls of a step are independent of one another, so a step may run them side by side: they are
-    # dealt over `lanes` streams (longest first, each to the least loaded lane) that become parallel
-    # branches of the step's CUDA graph.  While one call is in its short latency-bound phases (activation
-    # quantization, the cluster reduction) the others keep HBM busy.  lanes = 1 is the plain one-after-the-
-    # other order, timed as well: the per-launch roofline figure comes from that pass.
-    n_lanes = 1 if tp_mode == "nccl" else max(1, args.lanes)  # one communicator: its collectives stay in order
-    lane_streams = [torch.cuda.Stream(dev) for _ in range(n_lanes)]
-    # calls that may overlap on the GPU need separate workspaces
-    lane_ws = [pkg.llmops.Workspace(ws.nbytes, dev) for _ in range(n_lanes)]
-
-    def deal(n: int):
-        load, plan = [0.0] * n, [[] for _ in range(n)]
-        for c in sorted(calls, key=lambda c: -packed_bytes(c["K"], c["n_local"])):
-            i = load.index(min(load))
-            plan[i].append(c)
-            load[i] += packed_bytes(c["K"], c["n_local"]) / 5e12 + 4e-6 * (1 + c["M"] / 8)
-        return plan
-
-    def run_calls(cs, pdl: bool = True, wsp=None, side_by_side: bool = False) -> None:
-        outs = []
-        wsp = ws if wsp is None else wsp
-        for c in cs:
+            c = {"x": x, "wq": wq, "N": N, "n_local": n1 - n0, "M": M, "K": K}
             if fused:
-                outs.append((c, c["layer"](c["x"])))
+                c["layer"] = tp.FusedTPLinearQ4(sweep_sched, wq, N, max_rows=8, pdl=True, prequant=True)
+                c["y_full"] = torch.empty((1, M, N), device=dev, dtype=torch.float32)
             elif distributed:
-                c["layer"](c["x"])
+                c["layer"] = tp.TPLinearQ4(wq, N, pdl=True, path="decode")
             else:
-                pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=wsp, pdl=pdl, path="decode",
-                                  prequant=side_by_side)
-        # fused: unpack to plain fp32 behind the lane's FCs (each unpacking kernel waits for the other ranks'
-        # columns), so that the step ends when every rank holds every full output
-        for c, o in outs:
-            o.tensor(out=c["y_full"])
+                c["xq"] = ops.QuantizedActivations(1, M, K, GROUP_K, False, dev)
+                c["y"] = torch.empty((1, M, N), device=dev, dtype=torch.float32)
+            calls.append(c)
+    torch.cuda.synchronize()
+    per_rank_weight = sum(packed_bytes(c["K"], c["n_local"]) for c in calls)
+    per_rank_algo = sum(packed_bytes(c["K"], c["n_local"]) + 4 * c["M"] * c["K"] + 4 * c["M"] * c["n_local"]
+                        for c in calls)
 
-    def step_device(lanes: int = n_lanes) -> None:
-        cur = torch.cuda.current_stream(dev)
-        if fused:
+    # ---- the step
+    n_fc_launches = len(calls)
+    if not distributed:
+        # one launch per row count: calls of a launch then share the size of their code buffers
+        groups = [[c for c in calls if c["M"] == M] for M in MS]
+        batches = [ops.FCBatch([(c["xq"], c["wq"], c["N"], c["y"]) for c in g_], pdl=True) for g_ in groups]
+        n_fc_launches = len(batches)
+        side = torch.cuda.Stream(dev)
+
+        def step_device() -> None:
+            # the quantizers run on a side branch of the graph, group by group: all but the first group's hide
+            # behind the FCs of the group before
+            cur = torch.cuda.current_stream(dev)
+            start = torch.cuda.Event()
+            start.record(cur)
+            side.wait_event(start)
+            done = []
+            with torch.cuda.stream(side):
+                for g_ in groups:
+                    for c in g_:
+                        ops.quantize_activations(c["x"], GROUP_K, out=c["xq"])
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                    done.append(ev)
+            for b, ev in zip(batches, done):
+                cur.wait_event(ev)
+                b.run()
+
+        def step_fc_only() -> None:
+            for b in batches:
+                b.run()
+
+        launches_per_step = len(calls) + len(batches)
+    elif fused:
+        def step_device() -> None:
             sweep_sched.step_begin()
-        if lanes == 1:
-            # plain launches, each after the one before has finished: nothing of one launch hides in another
-            run_calls(calls, pdl=distributed or n_lanes == 1)
-            return
-        start = torch.cuda.Event()
-        start.record(cur)
-        for st, cs, wsp in zip(lane_streams, deal(lanes), lane_ws):
-            st.wait_event(start)
-            with torch.cuda.stream(st):
-                run_calls(cs, wsp=wsp, side_by_side=True)
-        for st in lane_streams[:lanes]:
-            cur.wait_stream(st)
+            outs = [(c, c["layer"](c["x"])) for c in calls]
+            # unpack to plain fp32 (each unpacking kernel waits for the other ranks' columns), so that the step
+            # ends when every rank holds every full output
+            for c, o in outs:
+                o.tensor(out=c["y_full"])
 
-    def capture(fn):
-        """Two eager runs (kernel attributes, TP buffers), then one CUDA graph of fn; fn itself if capture fails."""
-        for _ in range(2):
-            fn()
-        torch.cuda.synchronize()
-        try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                fn()
-            torch.cuda.synchronize()
-            return g.replay, True
-        except Exception as e:  # capture is an optimisation; eager launches still measure the same kernels
-            print(f"[bench] CUDA graph capture failed, timing eager launches: {e}", file=sys.stderr)
-            torch.cuda.synchronize()
-            return fn, False
+        step_fc_only = step_device
+        launches_per_step = 3 * len(calls) + 1  # quantizer, FC, unpacking per call; the step barrier
+    else:
+        def step_device() -> None:
+            for c in calls:
+                c["layer"](c["x"])
 
-    run_step, graphed = capture(step_device)
+        step_fc_only = step_device
+        launches_per_step = len(calls)
 
-    def barrier() -> None:
-        if distributed:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        run_step()
-    sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        run_step()
-    e1.record()
-    barrier()
-    clocks = sampler.stop()
-    if clocks["samples"] < 5:
-        # the timed region was shorter than a few NVML polls: keep replaying the same graph (untimed)
-        # for about a second and sample the clocks under that identical load
-        sampler = ClockSampler(local_rank)
-        sampler.start()
-        t_end = time.perf_counter() + 1.0
-        while time.perf_counter() < t_end:
-            for _ in range(50):
-                run_step()
-            torch.cuda.synchronize()
-        more = sampler.stop()
-        more["note"] = "sampled during an untimed one-second replay of the timed graph (timed region too short to poll)"
-        clocks = more
-    ms_total = e0.elapsed_time(e1)
+    run_step = capture(step_device)
+    # the timed region: args.steps steps, each replayed `inner` times so that the region lasts about half a second
+    probe_ms, _ = timed(run_step, 20, warm=warmup)
+    inner = max(1, int(round(TIMED_REGION_S * 1e3 / max(probe_ms * args.steps, 1e-6))))
     if distributed:
-        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+        t = torch.tensor([inner], device=dev, dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the same count on every rank: the step holds a cross-rank barrier
+        inner = int(t.item())
+
+    def run_steps() -> None:
+        for _ in range(inner):
+            run_step()
+
+    ms_outer, clocks = timed(run_steps, args.steps, warm=1, sample_clocks=True)
+    ms_step = ms_outer / inner
     value = STEP_WEIGHT_BYTES / (ms_step * 1e-3) / 1e9
+    section_status("sweep")
 
-    # ---- the same 16 launches one after the other on one stream: the per-launch figure of the roofline
-    ms_serial, serial_graphed = ms_step, graphed
-    if n_lanes > 1:
-        run_serial, serial_graphed = capture(lambda: step_device(1))
-        n_serial = max(3, min(args.steps, 500))
-        for _ in range(3):
-            run_serial()
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
-        for _ in range(n_serial):
-            run_serial()
-        s1.record()
-        barrier()
-        ms_serial = s0.elapsed_time(s1)
-        if distributed:
-            t = torch.tensor([ms_serial], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_serial = float(t.item())
-        ms_serial /= n_serial
+    # ---- the dominant kernel alone: the FC launches of a step with their inputs already quantized
+    if not distributed:
+        run_fc = capture(step_fc_only)
+        n_fc = max(20, min(2000, int(0.2e3 / max(probe_ms, 1e-3))))
+        ms_fc, _ = timed(run_fc, n_fc)
+    else:
+        ms_fc = ms_step
+    achieved = per_rank_algo / (ms_fc * 1e-3) / 1e9
 
-    # ---- end to end: host buffers in, host buffers out, every call (eager, public API)
+    # ---- every (shape, M) as a single call in order, on rotating distinct weights (ops/perf_ops.py:190-245)
+    per_call = None
+    ms_in_order = None
+    if not distributed and "percall" in sections:
+        ws = ops.Workspace(int(pkg._cabi.lib().q4fc_fc_workspace_bytes(8, 11008, 32000, QTYPE, GROUP_K)), dev)
+        per_call = {}
+        for pdl in (False, True):
+            def in_order() -> None:
+                for c in calls:
+                    ops.fc_Q4A(c["x"], c["wq"], c["N"], out=c["y"], workspace=ws, pdl=pdl, path="decode")
+            ms, _ = timed(capture(in_order), 200)
+            per_call["sweep_in_order_pdl_ms" if pdl else "sweep_in_order_plain_ms"] = ms
+        ms_in_order = per_call["sweep_in_order_pdl_ms"]
+
+    # ---- end to end: host buffers in, host buffers out, one copy each way per step (public API)
     e2e = None
     if "e2e" in sections:
-        hosts = []
-        for c in calls:
-            if fused:
-                hosts.append(tp.HostFusedFC(arena, c["wq"], c["N"], max_rows=8, pdl=True, prequant=n_lanes > 1,
-                                            stream=lane_streams[len(hosts) % n_lanes]))
-            elif distributed:
-                hosts.append(None)
-            else:
-                hosts.append(HostFC(c["wq"], c["N"], max_rows=8, workspace=lane_ws[len(hosts) % n_lanes],
-                                    path="decode", prequant=n_lanes > 1, stream=lane_streams[len(hosts) % n_lanes]))
-        # the activations sit in the pinned input buffer of the call's host front end
-        xs_host = [c["x"].cpu().pin_memory() if h is None else h.x_staging(c["M"]).copy_(c["x"].cpu())
-                   for c, h in zip(calls, hosts)]
-        ys_host = [torch.empty((1, c["M"], c["N"]), dtype=torch.float32).pin_memory() for c in calls]
+        if not distributed:
+            hb = HostFCBatch([(c["wq"], c["N"], c["M"]) for c in calls])
+            for i, c in enumerate(calls):
+                hb.x_staging(i).copy_(c["x"].cpu())
 
-        from llama_cl_b200.host import HostFCGroup
+            def step_e2e() -> None:
+                hb(None, sync=True)
 
-        group = HostFCGroup(hosts) if all(h is not None for h in hosts) else None
+            h2d, d2h = hb.h2d_bytes(), hb.d2h_bytes()
+        else:
+            hosts = [tp.HostFusedFC(arena, c["wq"], c["N"], max_rows=8, pdl=True, prequant=True) if fused else None
+                     for c in calls]
+            xs_host = [c["x"].cpu().pin_memory() if h is None else h.x_staging(c["M"]).copy_(c["x"].cpu())
+                       for c, h in zip(calls, hosts)]
+            ys_host = [torch.empty((1, c["M"], c["N"]), dtype=torch.float32).pin_memory() for c in calls]
 
-        def step_e2e() -> None:
-            if group is not None:
-                # the step's 16 calls as one submission: copies in, kernels, copies out on the lanes' streams
-                group(xs_host, sync=True)
-                return
-            for c, xh, yh in zip(calls, xs_host, ys_host):  # NCCL form: eager, call by call
-                c["x"].copy_(xh, non_blocking=True)
-                y = c["layer"](c["x"])
-                yh.copy_(y, non_blocking=True)
-            torch.cuda.current_stream(dev).synchronize()
+            def step_e2e() -> None:
+                if fused:
+                    for h, xh in zip(hosts, xs_host):
+                        h(xh, sync=False)
+                    for h in hosts:
+                        h.stream.synchronize()
+                else:
+                    for c, xh, yh in zip(calls, xs_host, ys_host):
+                        c["x"].copy_(xh, non_blocking=True)
+                        yh.copy_(c["layer"](c["x"]), non_blocking=True)
+                    torch.cuda.current_stream(dev).synchronize()
 
-        n_e2e = max(3, min(args.steps, 200))
+            h2d = sum(4 * c["M"] * c["K"] for c in calls)
+            d2h = sum(4 * c["M"] * c["N"] for c in calls)
+        n_e2e = max(3, min(args.steps * inner, 300))
         for _ in range(3):
             step_e2e()
         barrier()
-        t0 = torch.cuda.Event(enable_timing=True)
-        t1 = torch.cuda.Event(enable_timing=True)
         wall0 = time.perf_counter()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for _ in range(n_e2e):
             step_e2e()
         t1.record()
         barrier()
         wall = (time.perf_counter() - wall0) * 1e3
-        ms_e2e = max(t0.elapsed_time(t1), 0.0)
-        if distributed:
-            t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_e2e = float(t.item())
-        e2e = {"value": STEP_WEIGHT_BYTES / (ms_e2e / n_e2e * 1e-3) / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": sum(4 * c["M"] * c["K"] for c in calls),
-               "d2h_bytes_per_step": sum(4 * c["M"] * c["N"] for c in calls),
-               "ms_per_step": ms_e2e / n_e2e, "steps": n_e2e, "wall_ms_per_step": wall / n_e2e}
+        ms_e2e = max_over_ranks(max(t0.elapsed_time(t1), wall)) / n_e2e  # the host waits for every result
+        e2e = {"value": STEP_WEIGHT_BYTES / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "steps": n_e2e,
+               "api": "host.HostFCBatch: one pinned block and one copy each way per step" if not distributed else
+                      ("tp.HostFusedFC per call" if fused else "TPLinearQ4 with explicit copies")}
+        section_status("e2e")
 
     # ---- per-token pass through the FC stack of a 32-layer Llama-7B (225 FCs, batch 1)
     stack = None
-    try:
-        if "stack" not in sections:
-            raise RuntimeError("section not requested")
-        H, I, V, L = 4096, 11008, 32000, 32
+    if "stack" in sections:
+        try:
+            H, I, V, L = 4096, 11008, 32000, 32
 
-        def make_fc(N, K, seed):
-            """-> (fn(x) -> y, packed bytes on this rank)"""
-            gen.manual_seed(seed)
-            n0, n1 = tp.shard_rows(N, world, rank) if distributed else (0, N)
-            Wf = torch.randn((N, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
-            wq_ = pkg.llmops.offline_FC_quant_Q4A(Wf[n0:n1].contiguous(), qtype="q4_1", group_k=GROUP_K)
-            del Wf
-            if fused:
-                return make_layer(tok_sched, wq_, N, max_rows=1), wq_.numel()
-            if distributed:
-                return make_layer(None, wq_, N), wq_.numel()
-            return _LocalFC(wq_, N), wq_.numel()
+            def shard_pack(N, K, seed):
+                gen.manual_seed(seed)
+                n0, n1 = tp.shard_rows(N, world, rank) if distributed else (0, N)
+                Wf = torch.randn((N, K), generator=gen, device=dev, dtype=torch.float32) * 0.02
+                w = ops.offline_FC_quant_Q4A(Wf[n0:n1].contiguous(), qtype="q4_1", group_k=GROUP_K)
+                del Wf
+                return w
 
-        ws_of_stream: dict = {}
+            names = [("q", H, H), ("k", H, H), ("v", H, H), ("o", H, H), ("gate", I, H), ("up", I, H), ("down", H, I)]
+            layers = [{nm: shard_pack(N_, K_, 50000 + li * 16 + j) for j, (nm, N_, K_) in enumerate(names)}
+                      for li in range(L)]
+            lm_head = shard_pack(V, H, 49999)
+            full_bytes = sum(packed_bytes(K_, N_) for _, N_, K_ in names) * L + packed_bytes(H, V)
+            gen.manual_seed(7)
+            h0 = torch.randn((1, 1, H), generator=gen, device=dev, dtype=torch.float32)
+            stack = {"packed_weight_bytes": full_bytes, "fc_calls": 7 * L + 1,
+                     "what": "Q4_1 group-128 FC stack of a random-init 32-layer Llama-7B (hidden 4096, intermediate "
+                             "11008, vocab 32000 lm_head), batch 1"}
+            if not distributed:
+                for glue in ("none", "llama"):
+                    st = DecodeFCStack(layers, lm_head, hidden=H, intermediate=I, vocab=V, rows=1, glue=glue)
+                    st.forward(h0, sync=True)
+                    n_tok = max(3, min(args.steps * inner, 100))
+                    with torch.cuda.stream(st.stream):
+                        for _ in range(3):
+                            st.forward()
+                        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a0.record()
+                        for _ in range(n_tok):
+                            st.forward()
+                        a1.record()
+                    st.stream.synchronize()
+                    ms_tok = a0.elapsed_time(a1) / n_tok
+                    key = "ms_per_token" if glue == "none" else "ms_per_token_with_norms_and_mlp_glue"
+                    stack[key] = ms_tok
+                    stack["launches_per_token" if glue == "none" else "launches_per_token_with_glue"] = \
+                        st.launches_per_token
+                    if glue == "none":
+                        stack["weight_gb_s"] = full_bytes / (ms_tok * 1e-3) / 1e9
+                        stack["frac_of_hbm_peak"] = stack["weight_gb_s"] / peak
+                    del st
+                stack["launch"] = ("stack.DecodeFCStack: one CUDA graph per token; ms_per_token is the FC-only chain "
+                                   "(q/k/v and gate/up one launch each), the second figure adds rmsnorm, residual adds "
+                                   "and silu*up between the FCs")
+            else:
+                tok_sched = tp.TPSchedule(arena) if fused else None
 
-        class _LocalFC:
-            """One FC of the stack on this GPU: on fp32 activations, or on activations quantized beforehand."""
+                def mk(w, N_):
+                    if fused:
+                        return tp.FusedTPLinearQ4(tok_sched, w, N_, max_rows=1, pdl=True)
+                    return tp.TPLinearQ4(w, N_, pdl=True, path="decode")
 
-            def __init__(self, wq_, N_):
-                self.wq, self.N = wq_, N_
-                self.out = torch.empty((1, 1, N_), device=dev, dtype=torch.float32)
+                lay = [{nm: mk(l[nm], N_) for nm, N_, _ in names} for l in layers]
+                head = mk(lm_head, V)
+                logits = torch.empty((1, 1, V), device=dev, dtype=torch.float32)
 
-            def __call__(self, x_):
-                return pkg.llmops.fc_Q4A(x_, self.wq, self.N, out=self.out, workspace=stream_ws(), pdl=True,
-                                         path="decode")
+                def token() -> None:
+                    # the seven FCs of chatllama/main.py:348-370 with their data dependences; the non-FC ops
+                    # between them are not part of this path
+                    h = h0
+                    if fused:
+                        tok_sched.step_begin()
+                    for f in lay:
+                        q = f["q"](h)
+                        f["k"](h)
+                        f["v"](h)
+                        o = f["o"](q)
+                        g_ = f["gate"](o)
+                        f["up"](o)
+                        h = f["down"](g_)
+                    y = head(h)
+                    if fused:
+                        y.tensor(out=logits)  # the token is done when every rank holds the whole logits row
 
-            def q8(self, xq_):
-                return pkg.llmops.fc_Q4A_q8(xq_, self.wq, self.N, out=self.out, pdl=True)
+                run_tok = capture(token) if fused else token
+                ms_tok, _ = timed(run_tok, max(3, min(args.steps * inner, 60)))
+                stack["ms_per_token"] = ms_tok
+                stack["weight_gb_s"] = full_bytes / (ms_tok * 1e-3) / 1e9
+                stack["launch"] = "cuda graph of one token (225 fused N-split FCs)" if fused else "eager, NCCL all-gather per FC"
+                del lay, head
+            del layers, lm_head
+        except Exception as e:
+            stack = {"error": str(e)}
+        section_status("fc_stack")
 
-        def stream_ws():
-            """One workspace per stream: FCs running side by side must not share scratch."""
-            key = torch.cuda.current_stream(dev).cuda_stream
-            if key not in ws_of_stream:
-                ws_of_stream[key] = pkg.llmops.Workspace(ws.nbytes, dev)
-            return ws_of_stream[key]
+    # ---- the NCCL all-gather join named by the task, timed beside the fused form (short pass)
+    tp_nccl = None
+    if distributed and fused and "nccl" in sections:
+        try:
+            lay = [tp.TPLinearQ4(c["wq"], c["N"], pdl=True, path="decode") for c in calls]
 
-        tok_sched = tp.TPSchedule(arena) if fused else None
-        layers, stack_bytes_rank = [], 0
-        for li in range(L):
-            fcs = {}
-            for j, (name, N_, K_) in enumerate([("q", H, H), ("k", H, H), ("v", H, H), ("o", H, H),
-                                                ("gate", I, H), ("up", I, H), ("down", H, I)]):
-                fcs[name], nb = make_fc(N_, K_, 50000 + li * 16 + j)
-                stack_bytes_rank += nb
-            layers.append(fcs)
-        lm_head, nb = make_fc(V, H, 49999)
-        logits = torch.empty((1, 1, V), device=dev, dtype=torch.float32)
-        stack_bytes_rank += nb
-        gen.manual_seed(7)
-        h0 = torch.randn((1, 1, H), generator=gen, device=dev, dtype=torch.float32)
+            def step_nccl() -> None:
+                for c, l in zip(calls, lay):
+                    l(c["x"])
 
-        side = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
-
-        def fork(fns, x_):
-            """Run independent FCs of one input side by side: the first on the current stream, the rest on side
-            streams (they become parallel branches of the captured graph); returns their outputs after the join."""
-            cur = torch.cuda.current_stream(dev)
-            start = torch.cuda.Event()
-            start.record(cur)
-            outs = [None] * len(fns)
-            for i_, f_ in enumerate(fns[1:]):
-                with torch.cuda.stream(side[i_]):
-                    side[i_].wait_event(start)
-                    outs[i_ + 1] = f_(x_)
-            outs[0] = fns[0](x_)
-            for i_ in range(len(fns) - 1):
-                cur.wait_stream(side[i_])
-            return outs
-
-        def token() -> None:
-            # the seven FCs of chatllama/main.py:348-370 with their data dependences: q, k, v read the same
-            # input, as do gate and up; the non-FC ops between them are not part of this path
-            h = h0
-            if fused:
-                tok_sched.step_begin()
-            for f in layers:
-                q, _, _ = fork([f["q"], f["k"], f["v"]], h)
-                o = f["o"](q)
-                g_, _ = fork([f["gate"], f["up"]], o)
-                h = f["down"](g_)
-            y = lm_head(h)
-            if fused:
-                y.tensor(out=logits)  # the token is done when every rank holds the whole logits row
-
-        def time_token(fn):
-            run, graphed_ = capture(fn)
-            n_ = max(3, min(args.steps, 100))
-            for _ in range(3):
-                run()
-            barrier()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for _ in range(n_):
-                run()
-            a1.record()
-            barrier()
-            return a0.elapsed_time(a1), n_, graphed_
-
-        ms_tok, n_tok, tok_graphed = time_token(token)
-        if distributed:
-            t = torch.tensor([ms_tok], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_tok = float(t.item())
-        ms_tok /= n_tok
-        full_bytes = sum(packed_bytes(K_, N_) for N_, K_ in
-                         [(H, H)] * 4 + [(I, H)] * 2 + [(H, I)]) * L + packed_bytes(H, V)
-        stack = {"ms_per_token": ms_tok, "weight_gb_s": full_bytes / (ms_tok * 1e-3) / 1e9,
-                 "packed_weight_bytes": full_bytes, "fc_calls": 7 * L + 1, "tokens_timed": n_tok,
-                 "launch": "cuda graph of one token" if tok_graphed else "eager",
-                 "what": "Q4_1 group-128 FC stack of a random-init 32-layer Llama-7B (hidden 4096, intermediate "
-                         "11008, vocab 32000 lm_head), batch 1; FC kernels only"}
-        if not distributed:
-            # the same pass with every shared input quantized once (q/k/v read one quantized copy, gate/up
-            # another) instead of once per FC as the reference does
-            xq_a = pkg.llmops.QuantizedActivations(1, 1, H, GROUP_K, False, dev)
-            xq_b = pkg.llmops.QuantizedActivations(1, 1, H, GROUP_K, False, dev)
-
-            def token_quantize_once() -> None:
-                h = h0
-                for f in layers:
-                    xa = pkg.llmops.quantize_activations(h, GROUP_K, pdl=True, out=xq_a)
-                    q, _, _ = fork([f["q"].q8, f["k"].q8, f["v"].q8], xa)
-                    o = f["o"](q)
-                    xb = pkg.llmops.quantize_activations(o, GROUP_K, pdl=True, out=xq_b)
-                    g_, _ = fork([f["gate"].q8, f["up"].q8], xb)
-                    h = f["down"](g_)
-                lm_head(h)
-
-            ms_once, n_once, _ = time_token(token_quantize_once)
-            stack["ms_per_token_quantize_once"] = ms_once / n_once
-        del layers, lm_head
-    except Exception as e:
-        stack = {"error": str(e)}
+            ms_n, _ = timed(step_nccl, 30)
+            tp_nccl = {"ms_per_step": ms_n, "value": STEP_WEIGHT_BYTES / (ms_n * 1e-3) / 1e9, "unit": UNIT,
+                       "what": "the same sweep with every FC's column slices joined by an NCCL all-gather (eager launches)"}
+            # prefill under the N-split: M = 512, K = 4096, N = 11008, Q4_1 group 128, all-gather of [M, N/g] tiles
+            gen.manual_seed(4243)
+            Wp = torch.randn((11008, 4096), generator=gen, device=dev, dtype=torch.float32) * 0.02
+            lp = tp.TPLinearQ4.from_full_weight(Wp, qtype="q4_1", group_k=GROUP_K)
+            xp = torch.randn((1, 512, 4096), generator=gen, device=dev, dtype=torch.float32)
+            ms_p, _ = timed(lambda: lp(xp), 10)
+            tp_nccl["prefill_M512_K4096_N11008_ms"] = ms_p
+            tp_nccl["prefill_M512_tops"] = 2.0 * 512 * 11008 * 4096 / (ms_p * 1e-3) / 1e12
+            del Wp, lp
+        except Exception as e:
+            tp_nccl = {"error": str(e)}
 
     # ---- the other configurations of the path, reported beside the headline (single GPU only)
     extras = None
@@ -612,7 +620,7 @@ def our_arm(args) -> None:
             gen.manual_seed(4242)
             Wp = torch.randn((11008, 4096), generator=gen, device=dev, dtype=torch.float32) * 0.02
 
-            def timed(fn, reps):
+            def time_fn(fn, reps):
                 fn()
                 torch.cuda.synchronize()
                 t0_, t1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -623,25 +631,28 @@ def our_arm(args) -> None:
                 torch.cuda.synchronize()
                 return t0_.elapsed_time(t1_) / reps
 
-            # prefill: Q4_0 group 32, K=4096, N=11008, M=512 and 2048 (int8 tensor-core kernel + quantizer)
-            wq0 = pkg.llmops.offline_FC_quant_Q4A(Wp, qtype="q4_0", group_k=32)
-            pre = {}
-            for M_ in (512, 2048):
-                xp = torch.randn((1, M_, 4096), generator=gen, device=dev, dtype=torch.float32)
-                yp = torch.empty((1, M_, 11008), device=dev, dtype=torch.float32)
-                wsp = pkg.llmops.fc_workspace(M_, 4096, 11008, 0, 32, dev)
-                ms_ = timed(lambda: pkg.llmops.fc_Q4A(xp, wq0, 11008, out=yp, workspace=wsp), 10)
-                wsp.check()
-                pre[f"M{M_}"] = {"ms": ms_, "tops": 2.0 * M_ * 11008 * 4096 / (ms_ * 1e-3) / 1e12}
-            extras["prefill_q4_0_g32_K4096_N11008"] = pre
-            # packer: fp32 -> Q4_1, one 11008x4096 matrix (algorithmic bytes = 4 B read + packed bytes written per weight)
-            pk = {}
-            for G_ in (32, 128):
-                outp = torch.empty(((11008 + 31) // 32, 4096 // G_, 16 * G_ + 128), dtype=torch.int8, device=dev)
-                ms_ = timed(lambda: pkg.llmops.offline_FC_quant_Q4A(Wp, qtype="q4_1", group_k=G_, out=outp), 20)
-                nbytes = Wp.numel() * 4 + outp.numel()
-                pk[f"g{G_}"] = {"ms": ms_, "gb_s": nbytes / (ms_ * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_ * 1e-3) / 1e9 / load_peaks()[0]}
-            extras["pack_q4_1_11008x4096"] = pk
+            # prefill: K=4096, N=11008, M=512 and 2048 (int8 tensor-core kernel + quantizer), Q4_0 g32 (the baseline's
+            # configuration) and Q4_1 g128 (the format of the decode configurations)
+            int8_peak_tops = 2.0 * 1641.8
+            try:
+                with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                    int8_peak_tops = 2.0 * float(json.load(f)["bf16_tflops"])
+            except Exception:
+                pass
+            for qname, G_ in (("q4_0", 32), ("q4_1", 128)):
+                wq0 = ops.offline_FC_quant_Q4A(Wp, qtype=qname, group_k=G_)
+                pre = {}
+                for M_ in (512, 2048):
+                    xp = torch.randn((1, M_, 4096), generator=gen, device=dev, dtype=torch.float32)
+                    yp = torch.empty((1, M_, 11008), device=dev, dtype=torch.float32)
+                    wsp = ops.fc_workspace(M_, 4096, 11008, 0 if qname == "q4_0" else 1, G_, dev)
+                    ms_ = time_fn(lambda: ops.fc_Q4A(xp, wq0, 11008, out=yp, workspace=wsp), 10)
+                    wsp.check()
+                    tops = 2.0 * M_ * 11008 * 4096 / (ms_ * 1e-3) / 1e12
+                    pre[f"M{M_}"] = {"ms": ms_, "tops": tops, "frac_of_int8_peak": tops / int8_peak_tops}
+                pre["int8_peak_tops"] = int8_peak_tops
+                pre["int8_peak_kind"] = "2 x the measured dense bf16 burst figure (no int8 figure is measured on this pool)"
+                extras[f"prefill_{qname}_g{G_}_K4096_N11008"] = pre
             # packer over a whole Llama-7B FC weight set: 32 layers x {q, k, v, o: 4096x4096; gate, up: 11008x4096;
             # down: 4096x11008}, one matrix after the other (every fp32 matrix is 64-180 MB: nothing stays in L2)
             shapes_ = {(4096, 4096): 4 * 32, (11008, 4096): 2 * 32, (4096, 11008): 1 * 32}
@@ -654,16 +665,15 @@ def our_arm(args) -> None:
                 def pack_all():
                     for sh, cnt in shapes_.items():
                         for _ in range(cnt):
-                            pkg.llmops.offline_FC_quant_Q4A(mats_[sh], qtype="q4_1", group_k=G_, out=outs_[sh])
+                            ops.offline_FC_quant_Q4A(mats_[sh], qtype="q4_1", group_k=G_, out=outs_[sh])
 
-                ms_ = timed(pack_all, 3)
+                ms_ = time_fn(pack_all, 3)
                 nbytes = sum(cnt * (mats_[sh].numel() * 4 + outs_[sh].numel()) for sh, cnt in shapes_.items())
-                full[f"g{G_}"] = {"ms": ms_, "gb_s": nbytes / (ms_ * 1e-3) / 1e9, "weights": sum(
-                    cnt * mats_[sh].numel() for sh, cnt in shapes_.items()),
-                    "frac_of_hbm_peak": nbytes / (ms_ * 1e-3) / 1e9 / load_peaks()[0]}
+                full[f"g{G_}"] = {"ms": ms_, "gb_s": nbytes / (ms_ * 1e-3) / 1e9,
+                                  "weights": sum(cnt * mats_[sh].numel() for sh, cnt in shapes_.items()),
+                                  "frac_of_hbm_peak": nbytes / (ms_ * 1e-3) / 1e9 / peak}
             extras["pack_q4_1_llama7b_fc_set_224_matrices"] = full
-            del mats_
-            del Wp
+            del mats_, Wp
         except Exception as e:
             extras = {"error": str(e)}
 
@@ -671,10 +681,10 @@ def our_arm(args) -> None:
     check = None
     y_tp = None
     if distributed:
-        # one more untimed step; every rank must now hold the same full output of the first call
         c = calls[0]
         if fused:
             step_device()
+            torch.cuda.synchronize()
             y_tp = c["y_full"].reshape(c["M"], c["N"]).clone()
         else:
             y_tp = c["layer"](c["x"]).reshape(c["M"], c["N"]).clone()
@@ -682,39 +692,28 @@ def our_arm(args) -> None:
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         ranks_agree = bool(torch.equal(lo, hi))
+        section_status("spot_check")
     if rank == 0:
         import numpy as np
 
         from oracle import cpu
 
-        c = calls[0]
         if not distributed:
-            y = pkg.llmops.fc_Q4A(c["x"], c["wq"], c["N"], workspace=ws).cpu().numpy()
-            want = cpu.restated.fc(c["x"].cpu().numpy(), c["wq"].cpu().numpy(), c["N"])
-            check = bool(np.allclose(y, want, rtol=1e-3, atol=1e-4))
+            run_step()
+            torch.cuda.synchronize()
+            check = True
+            for c in (calls[0], calls[7], calls[15]):
+                want = cpu.restated.fc(c["x"].cpu().numpy(), c["wq"].cpu().numpy(), c["N"])
+                check = check and bool(np.allclose(c["y"].cpu().numpy(), want, rtol=1e-3, atol=1e-4))
         else:
-            # this rank's own columns against the CPU restatement of its shard, and all ranks bit-equal
+            c = calls[0]
+            n0, _ = tp.shard_rows(c["N"], world, rank)
             want = cpu.restated.fc(c["x"].cpu().numpy(), c["wq"].cpu().numpy(), c["n_local"])
-            mine = y_tp[:, : c["n_local"]].cpu().numpy().reshape(want.shape)
+            mine = y_tp[:, n0: n0 + c["n_local"]].cpu().numpy().reshape(want.shape)
             check = bool(np.allclose(mine, want, rtol=1e-3, atol=1e-4)) and ranks_agree
 
-    tp_status = arena.status() if fused else 0  # non-zero: a bounded wait on another rank ran out
-    # this library's kernels per timed step: the FC kernel of every call, plus -- side by side on one GPU --
-    # the quantizing launch in front of each, or -- N-split -- the step barrier and one unpacking kernel per call
-    if fused:
-        launches_per_step = (3 if n_lanes > 1 else 2) * len(calls) + 1
-    elif distributed:
-        launches_per_step = len(calls)
-    elif n_lanes > 1:
-        launches_per_step = 2 * len(calls)
-    else:
-        launches_per_step = len(calls) + sum(1 for c in calls if c["M"] * c["K"] >= 40 * 1024)
+    bad_status = {k: v for k, v in status_words.items() if v != 0}
     if rank == 0:
-        peak, peak_kind = load_peaks()
-        # per launch: the step's algorithmic bytes and time divided by its 16 launches
-        per_rank_algo = sum(packed_bytes(c["K"], c["n_local"]) + 4 * c["M"] * c["K"] + 4 * c["M"] * c["n_local"]
-                            for c in calls)
-        achieved = per_rank_algo / (ms_serial * 1e-3) / 1e9
         cpu_baseline = None
         if not distributed and "cpu" in sections:
             try:
@@ -725,46 +724,62 @@ def our_arm(args) -> None:
                 model, ncpu = host_cpu_info()
                 cpu_baseline = {"value": STEP_WEIGHT_BYTES / sec / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
                                 "sample": f"the whole 16-call sweep, {passes} passes (~{sec * passes:.0f} s); "
-                                          f"host CPU {model}, {ncpu} logical CPUs", "ms_per_step": sec * 1e3}
+                                          f"host CPU {model}, {ncpu} usable logical CPUs", "ms_per_step": sec * 1e3}
             except Exception as e:
                 cpu_baseline = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": "int8xuint4->int32, fp32 scaling", "data": "synthetic",
-            "config": dict(CONFIG, parallelism=(
-                "single GPU" if world == 1 else
-                f"N-split tp{world}, columns stored into every rank's buffer by the FC kernel (epoch-stamped 64-bit "
-                f"words, NVLink peer stores)" if fused else f"N-split tp{world} + NCCL all-gather"),
-                           **({"tp_note": tp_note} if tp_note else {}),
-                           launch=(f"cuda graph of one step, the 16 independent calls on {n_lanes} parallel branches"
-                                   if graphed else "eager"),
-                           lanes=n_lanes),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
-            **({"tp_status": tp_status} if fused else {}),
+            "dtype": "int8xuint4->int32, fp32 scaling", "data": "synthetic", "config": CONFIG,
+            "launch": {
+                "parallelism": (
+                    "single GPU" if world == 1 else
+                    f"N-split tp{world}, columns stored into every rank's buffer by the FC kernel (epoch-stamped "
+                    f"64-bit words, NVLink peer stores)" if fused else f"N-split tp{world} + NCCL all-gather"),
+                **({"tp_note": tp_note} if tp_note else {}),
+                "step": ("cuda graph: 16 quantizer launches on a side branch + 4 launches of q4fc_fc_decode_batch "
+                         "(one per row count)" if not distributed else "cuda graph of the 16 calls in order"
+                         if fused else "eager"),
+                "inner_repeats_per_step": inner, "timed_region_ms": ms_outer * args.steps},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps * inner,
+            "gpu_launches_per_step": launches_per_step,
+            **({"tp_status": max(status_words.values()) if status_words else 0, "tp_status_sections": status_words}
+               if fused else {}),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": DECODE_TRAFFIC_PER_LAUNCH if not distributed else None,
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average over the decode "
-                                           "launches of this sweep (launch-list summary under profiles/)",
-                         "peak_kind": peak_kind,
-                         "kernel": "fc_decode_cluster_kernel<128,1,false,ROWS>",
-                         "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": len(calls),
-                         "timed_as": "the 16 launches one after the other on one stream, plain stream order (a "
-                                     "second timed pass); average launch duration = pass time / 16",
-                         "ms_per_step_serial": ms_serial,
-                         "value_serial": STEP_WEIGHT_BYTES / (ms_serial * 1e-3) / 1e9},
-            "cpu_baseline": cpu_baseline, "parity_spot_check": check, "fc_stack": stack, "other_configs": extras,
+                         "frac": achieved / peak,
+                         "traffic": (DECODE_TRAFFIC_RATIO * per_rank_algo / n_fc_launches) if not distributed else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the step's FC launches "
+                                           "(summary under profiles/), per launch",
+                         "peak_kind": peak_kind, "kernel": "fc_decode_ring_kernel<128,1,false,8,false,true>",
+                         "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": n_fc_launches,
+                         "algorithmic_bytes_per_launch": per_rank_algo / n_fc_launches,
+                         "avg_launch_ms": ms_fc / n_fc_launches,
+                         "timed_as": "the step's FC launches alone (inputs already quantized), replayed as a graph; "
+                                     "average launch duration = pass time / launches",
+                         **({"in_order_single_calls": {
+                             "what": "the 16 calls as 16 single q4fc_fc_decode launches in order on one stream",
+                             "frac_pdl": per_rank_algo / (ms_in_order * 1e-3) / 1e9 / peak,
+                             "frac_plain": per_rank_algo / (per_call["sweep_in_order_plain_ms"] * 1e-3) / 1e9 / peak,
+                             **per_call}} if per_call else {})},
+            "cpu_baseline": cpu_baseline, "parity_spot_check": check, "fc_stack": stack,
+            **({"tp_nccl": tp_nccl} if tp_nccl is not None else {}),
+            "other_configs": extras,
         }
         _emit(json.dumps(line))
+    rc = 0
+    if bad_status or (rank == 0 and check is False):
+        print(f"[bench] INVALID RUN: status words {bad_status}, parity spot check {check}", file=sys.stderr)
+        rc = 1
     if distributed:
         # Captured graphs hold NCCL work; tearing the process group down under them has been seen to
-        # block.  Every collective of this run is behind us (the last one was the all-reduce of the
-        # timings): drain the GPU and leave without the interpreter's teardown.
+        # block.  Every collective of this run is behind us: drain the GPU and leave without the
+        # interpreter's teardown.
         torch.cuda.synchronize()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        os._exit(rc)
+    return rc
 
 
 def main() -> None:
@@ -777,20 +792,20 @@ def main() -> None:
     _emit = lambda line: (real_stdout.write(line + "\n"), real_stdout.flush())  # noqa: E731
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--lanes", type=int, default=4,
-                    help="parallel graph branches the 16 independent calls of a step are dealt over (1: in order)")
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
                     help="with --gpus N > 1: how the ranks' output columns meet")
-    ap.add_argument("--sections", default="e2e,stack,extras,cpu",
+    ap.add_argument("--sections", default="e2e,stack,extras,cpu,percall,nccl",
                     help="optional legs beside the timed sweep (a profiler run asks for none of them: --sections none)")
     args = ap.parse_args()
     if args.impl == "reference":
+        # a launcher may have exported OMP_NUM_THREADS=1 for its children: the reference arm uses every core it may
+        os.environ.pop("OMP_NUM_THREADS", None)
         reference_arm(args)
-    else:
-        our_arm(args)
+        sys.exit(0)
+    sys.exit(our_arm(args))
 
 
 if __name__ == "__main__":

@@ -79,10 +79,20 @@ def ref_lib_path(variant: str, isa: str) -> str:
     return os.path.join(REF_DIR, f"libref_{variant}_{isa}.so")
 
 
-def build_reference(reference_root: str = "/root/reference", force: bool = False) -> list[str]:
+def reference_root() -> str | None:
+    """Where the reference checkout lies: the environment variable Q4FC_REFERENCE, or --reference on the command line."""
+    return os.environ.get("Q4FC_REFERENCE") or None
+
+
+def build_reference(reference_root: str | None = None, force: bool = False) -> list[str]:
     """Compile the reference's FC for the four block variants x two ISAs.
 
-    Returns the list of libraries built (empty when the checkout is absent)."""
+    ``reference_root``: the reference checkout (default: the environment variable Q4FC_REFERENCE).  Returns the
+    list of libraries built (empty when no checkout is given or it is absent)."""
+    if reference_root is None:
+        reference_root = os.environ.get("Q4FC_REFERENCE")
+    if not reference_root:
+        return []
     ops = os.path.join(reference_root, "ops")
     hdr = os.path.join(ops, "op_fc.hpp")
     if not os.path.exists(hdr):
@@ -112,8 +122,11 @@ def build_reference(reference_root: str = "/root/reference", force: bool = False
 
 def main() -> None:
     force = "--force" in sys.argv
+    ref = None
+    if "--reference" in sys.argv:
+        ref = sys.argv[sys.argv.index("--reference") + 1]
     print(build_restatement(force))
-    for p in build_reference(force=force):
+    for p in build_reference(ref, force=force):
         print(p)
 
 

@@ -48,7 +48,7 @@ def build(reference: str, force: bool = False) -> str | None:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("Q4FC_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("Q4FC_REFERENCE"), required="Q4FC_REFERENCE" not in os.environ)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     p = build(a.reference, a.force)

@@ -193,6 +193,13 @@ class CompiledReference:
     def threads(self) -> int:
         return int(self.lib.ref_max_threads())
 
+    def set_threads(self, n: int) -> int:
+        """Size of the OpenMP team of later calls; returns what is in force (older builds of the checker
+        library have no setter: then the inherited OMP_NUM_THREADS stands)."""
+        if hasattr(self.lib, "ref_set_threads"):
+            return int(self.lib.ref_set_threads(int(n)))
+        return self.threads()
+
     def pack(self, w) -> np.ndarray:
         w = _f32(w)
         N, K = w.shape

@@ -28,7 +28,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("Q4FC_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("Q4FC_REFERENCE"), required="Q4FC_REFERENCE" not in os.environ)
     a = ap.parse_args()
     sys.path.insert(0, ROOT)
     from oracle import build_ref_module

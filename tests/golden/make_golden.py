@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this folder from the COMPILED REFERENCE.
 
-Run in a container that has the reference checkout (``/root/reference``):
+Run in a container that has the reference checkout (Q4FC_REFERENCE=/path/to/llama.cl):
 
     python oracle/build_oracle.py          # builds oracle/_ref from the reference sources
     python tests/golden/make_golden.py

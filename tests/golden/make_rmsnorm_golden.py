@@ -17,8 +17,10 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("Q4FC_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("Q4FC_REFERENCE"))
     a = ap.parse_args()
+    if not a.reference:
+        raise SystemExit("give --reference /path/to/llama.cl (or set Q4FC_REFERENCE)")
     sys.path.insert(0, ROOT)
     from oracle import build_ref_module
 
