@@ -338,7 +338,8 @@ def our_arm(args) -> int:
             x = torch.randn((1, M, K), generator=gen, device=dev, dtype=torch.float32)
             c = {"x": x, "wq": wq, "N": N, "n_local": n1 - n0, "M": M, "K": K}
             if fused:
-                c["layer"] = tp.FusedTPLinearQ4(sweep_sched, wq, N, max_rows=8, pdl=True, prequant=True)
+                c["layer"] = tp.FusedTPLinearQ4(sweep_sched, wq, N, max_rows=8, pdl=True)
+                c["xq"] = ops.QuantizedActivations(1, M, K, GROUP_K, False, dev)
                 c["y_full"] = torch.empty((1, M, N), device=dev, dtype=torch.float32)
             elif distributed:
                 c["layer"] = tp.TPLinearQ4(wq, N, pdl=True, path="decode")
@@ -385,16 +386,36 @@ def our_arm(args) -> int:
 
         launches_per_step = len(calls) + len(batches)
     elif fused:
+        groups = [[c for c in calls if c["M"] == M] for M in MS]
+        tbatches = [tp.FusedTPBatch([c["layer"] for c in g_], [c["xq"] for c in g_]) for g_ in groups]
+        side = torch.cuda.Stream(dev)
+
         def step_device() -> None:
+            # step barrier, the quantizers on a side branch group by group, one N-split launch per row count, and
+            # ONE unpacking launch that waits for the other ranks' columns of all 16 outputs: the step ends when
+            # every rank holds every full output
+            cur = torch.cuda.current_stream(dev)
+            start = torch.cuda.Event()
+            start.record(cur)
+            side.wait_event(start)
+            done = []
+            with torch.cuda.stream(side):
+                for g_ in groups:
+                    for c in g_:
+                        ops.quantize_activations(c["x"], GROUP_K, out=c["xq"])
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                    done.append(ev)
             sweep_sched.step_begin()
-            outs = [(c, c["layer"](c["x"])) for c in calls]
-            # unpack to plain fp32 (each unpacking kernel waits for the other ranks' columns), so that the step
-            # ends when every rank holds every full output
-            for c, o in outs:
-                o.tensor(out=c["y_full"])
+            outs = []
+            for b, ev in zip(tbatches, done):
+                cur.wait_event(ev)
+                outs += b.run()
+            tp.collect_many(outs, [c["y_full"] for g_ in groups for c in g_])
 
         step_fc_only = step_device
-        launches_per_step = 3 * len(calls) + 1  # quantizer, FC, unpacking per call; the step barrier
+        n_fc_launches = len(tbatches)
+        launches_per_step = len(calls) + len(tbatches) + 2  # quantizers, N-split launches, step barrier, unpacking
     else:
         def step_device() -> None:
             for c in calls:
@@ -457,26 +478,27 @@ def our_arm(args) -> int:
 
             h2d, d2h = hb.h2d_bytes(), hb.d2h_bytes()
         else:
-            hosts = [tp.HostFusedFC(arena, c["wq"], c["N"], max_rows=8, pdl=True, prequant=True) if fused else None
-                     for c in calls]
-            xs_host = [c["x"].cpu().pin_memory() if h is None else h.x_staging(c["M"]).copy_(c["x"].cpu())
-                       for c, h in zip(calls, hosts)]
-            ys_host = [torch.empty((1, c["M"], c["N"]), dtype=torch.float32).pin_memory() for c in calls]
+            if fused:
+                hbt = tp.HostFusedBatch(arena, [(c["wq"], c["N"], c["M"]) for c in calls])
+                for i, c in enumerate(calls):
+                    hbt.x_staging(i).copy_(c["x"].cpu())
 
-            def step_e2e() -> None:
-                if fused:
-                    for h, xh in zip(hosts, xs_host):
-                        h(xh, sync=False)
-                    for h in hosts:
-                        h.stream.synchronize()
-                else:
+                def step_e2e() -> None:
+                    hbt(None, sync=True, check=False)  # the status word is read once after the section
+
+                h2d, d2h = hbt.h2d_bytes(), hbt.d2h_bytes()
+            else:
+                xs_host = [c["x"].cpu().pin_memory() for c in calls]
+                ys_host = [torch.empty((1, c["M"], c["N"]), dtype=torch.float32).pin_memory() for c in calls]
+
+                def step_e2e() -> None:
                     for c, xh, yh in zip(calls, xs_host, ys_host):
                         c["x"].copy_(xh, non_blocking=True)
                         yh.copy_(c["layer"](c["x"]), non_blocking=True)
                     torch.cuda.current_stream(dev).synchronize()
 
-            h2d = sum(4 * c["M"] * c["K"] for c in calls)
-            d2h = sum(4 * c["M"] * c["N"] for c in calls)
+                h2d = sum(4 * c["M"] * c["K"] for c in calls)
+                d2h = sum(4 * c["M"] * c["N"] for c in calls)
         n_e2e = max(3, min(args.steps * inner, 300))
         for _ in range(3):
             step_e2e()
@@ -493,7 +515,8 @@ def our_arm(args) -> int:
         e2e = {"value": STEP_WEIGHT_BYTES / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "steps": n_e2e,
                "api": "host.HostFCBatch: one pinned block and one copy each way per step" if not distributed else
-                      ("tp.HostFusedFC per call" if fused else "TPLinearQ4 with explicit copies")}
+                      ("tp.HostFusedBatch: one pinned block and one copy each way per step, every rank" if fused
+                       else "TPLinearQ4 with explicit copies")}
         section_status("e2e")
 
     # ---- per-token pass through the FC stack of a 32-layer Llama-7B (225 FCs, batch 1)
@@ -559,11 +582,18 @@ def our_arm(args) -> int:
                 logits = torch.empty((1, 1, V), device=dev, dtype=torch.float32)
 
                 def token() -> None:
-                    # the seven FCs of chatllama/main.py:348-370 with their data dependences; the non-FC ops
-                    # between them are not part of this path
+                    # the seven FCs of chatllama/main.py:348-370 with their data dependences (q, k, v and gate, up as
+                    # one launch each); the non-FC ops between them are not part of this path
                     h = h0
                     if fused:
                         tok_sched.step_begin()
+                        for f in lay:
+                            q, _, _ = tp.fused_multi([f["q"], f["k"], f["v"]], h)
+                            o = f["o"](q)
+                            g_, _ = tp.fused_multi([f["gate"], f["up"]], o)
+                            h = f["down"](g_)
+                        head(h).tensor(out=logits)  # the token is done when every rank holds the whole logits row
+                        return
                     for f in lay:
                         q = f["q"](h)
                         f["k"](h)
@@ -572,15 +602,14 @@ def our_arm(args) -> int:
                         g_ = f["gate"](o)
                         f["up"](o)
                         h = f["down"](g_)
-                    y = head(h)
-                    if fused:
-                        y.tensor(out=logits)  # the token is done when every rank holds the whole logits row
+                    head(h)
 
                 run_tok = capture(token) if fused else token
                 ms_tok, _ = timed(run_tok, max(3, min(args.steps * inner, 60)))
                 stack["ms_per_token"] = ms_tok
                 stack["weight_gb_s"] = full_bytes / (ms_tok * 1e-3) / 1e9
-                stack["launch"] = "cuda graph of one token (225 fused N-split FCs)" if fused else "eager, NCCL all-gather per FC"
+                stack["launch"] = ("cuda graph of one token (225 fused N-split FCs in 129 launches)" if fused
+                                   else "eager, NCCL all-gather per FC")
                 del lay, head
             del layers, lm_head
         except Exception as e:
@@ -739,8 +768,9 @@ def our_arm(args) -> int:
                     f"64-bit words, NVLink peer stores)" if fused else f"N-split tp{world} + NCCL all-gather"),
                 **({"tp_note": tp_note} if tp_note else {}),
                 "step": ("cuda graph: 16 quantizer launches on a side branch + 4 launches of q4fc_fc_decode_batch "
-                         "(one per row count)" if not distributed else "cuda graph of the 16 calls in order"
-                         if fused else "eager"),
+                         "(one per row count)" if not distributed else
+                         "cuda graph: step barrier, 16 quantizer launches on a side branch, 4 launches of "
+                         "q4fc_fc_decode_tp_batch (one per row count), one unpacking launch" if fused else "eager"),
                 "inner_repeats_per_step": inner, "timed_region_ms": ms_outer * args.steps},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps * inner,
             "gpu_launches_per_step": launches_per_step,

@@ -300,6 +300,25 @@ int q4fc_fc_decode_tp(const void* x, int64_t rows, int64_t K, int64_t ldx, const
                       int qtype, int group_k, int64_t N, int64_t ldy, const q4fc_tp_site* site, unsigned flags,
                       q4fc_stream_t stream);
 
+/* Up to four N-split FCs as ONE launch (q/k/v, gate/up, or four independent calls of a batch).  Call i stores
+ * into sites[i]->y_peer at sites[i]->col_off; world, epoch, status and x_stamped are taken from sites[0] and
+ * must be the same in all.  Inputs: every call its own pre-quantized xq (x = NULL), or all calls the same x
+ * (fp32 [rows][ldx], or a stamped buffer with sites[0]->x_stamped), quantized inside the kernel. */
+typedef struct q4fc_tp_call {
+    const void* x;   /* fp32 / stamped input shared by all calls, or NULL */
+    const void* xq;  /* pre-quantized input of this call, or NULL */
+    int64_t rows, K, ldx;
+    const void* wq;  /* this rank's stripes [Ng][Kg][BS] */
+    int64_t Ng, Kg, N, ldy;
+} q4fc_tp_call;
+int q4fc_fc_decode_tp_batch(const q4fc_tp_call* calls, const q4fc_tp_site* const* sites, int ncalls, int qtype,
+                            int group_k, unsigned flags, q4fc_stream_t stream);
+/* q4fc_tp_collect for up to 16 stamped buffers in one launch.  dst[i] may be NULL: then the launch only waits until
+ * every word of buffer i carries the current epoch (the step's hand-over to consumers that read stamped words). */
+int q4fc_tp_collect_multi(const unsigned long long* const* stamped, const int64_t* rows, const int64_t* N,
+                          const int64_t* ld, float* const* dst, const int64_t* ldd, int n,
+                          const unsigned long long* epoch, int* status, q4fc_stream_t stream);
+
 /* Reads and clears the device status word kept at the start of a workspace
  * (host-synchronous: waits for `stream`).  ws = NULL reads the word that decode
  * calls made without a workspace share (one per device).  Returns Q4FC_OK or

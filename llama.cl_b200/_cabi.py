@@ -25,6 +25,7 @@ SYMBOLS = (
     "q4fc_fc_decode_add", "q4fc_fc_decode_multi", "q4fc_fc_decode_batch",
     "q4fc_tp_arena_create", "q4fc_tp_arena_open", "q4fc_tp_arena_close", "q4fc_tp_arena_destroy",
     "q4fc_tp_step_begin", "q4fc_tp_collect", "q4fc_fc_decode_tp", "q4fc_tp_site_bytes",
+    "q4fc_fc_decode_tp_batch", "q4fc_tp_collect_multi",
     "q4fc_xq_bytes", "q4fc_quant_x_q8", "q4fc_rmsnorm_quant", "q4fc_add_rmsnorm_quant", "q4fc_fc_decode_q8",
     "q4fc_silu_mul_quant",
 )
@@ -54,6 +55,22 @@ class FcJob(C.Structure):
         ("ldy", C.c_int64),
         ("addend", C.c_void_p),
         ("ld_addend", C.c_int64),
+    ]
+
+
+class TpCall(C.Structure):
+    """``q4fc_tp_call`` of include/q4fc_b200.h."""
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("xq", C.c_void_p),
+        ("rows", C.c_int64),
+        ("K", C.c_int64),
+        ("ldx", C.c_int64),
+        ("wq", C.c_void_p),
+        ("Ng", C.c_int64),
+        ("Kg", C.c_int64),
+        ("N", C.c_int64),
+        ("ldy", C.c_int64),
     ]
 
 
@@ -124,6 +141,9 @@ def lib() -> C.CDLL:
     L.q4fc_tp_step_begin.argtypes = [vp, C.POINTER(vp), vp, i32, vp, vp]
     L.q4fc_tp_collect.argtypes = [vp, i64, i64, i64, vp, i64, vp, vp, vp]
     L.q4fc_fc_decode_tp.argtypes = [vp, i64, i64, i64, vp, i64, i64, i32, i32, i64, i64, C.POINTER(TpSite), u32, vp]
+    L.q4fc_fc_decode_tp_batch.argtypes = [C.POINTER(TpCall), C.POINTER(C.POINTER(TpSite)), i32, i32, i32, u32, vp]
+    L.q4fc_tp_collect_multi.argtypes = [C.POINTER(vp), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), C.POINTER(vp),
+                                        C.POINTER(i64), i32, vp, vp, vp]
     _lib = L
     return L
 

@@ -575,6 +575,71 @@ int q4fc_fc_decode_tp(const void* x, int64_t rows, int64_t K, int64_t ldx, const
                                        static_cast<cudaStream_t>(stream), site);
 }
 
+int q4fc_fc_decode_tp_batch(const q4fc_tp_call* calls, const q4fc_tp_site* const* sites, int ncalls, int qtype,
+                            int group_k, unsigned flags, q4fc_stream_t stream) {
+    if (!calls || !sites || ncalls < 1 || ncalls > 4) {
+        set_error("fc_decode_tp_batch: null argument or ncalls=%d outside 1..4", ncalls);
+        return Q4FC_EINVAL;
+    }
+    if (flags & Q4FC_FLAG_STREAMK) {
+        set_error("fc_decode_tp_batch: Q4FC_FLAG_STREAMK is not available for the multi-GPU form");
+        return Q4FC_EINVAL;
+    }
+    for (int i = 0; i < ncalls; i++) {
+        const q4fc_tp_call& c = calls[i];
+        const q4fc_tp_site* t = sites[i];
+        if (!t || t->world < 1 || t->world > 8 || !t->epoch || !t->status || t->world != sites[0]->world ||
+            t->epoch != sites[0]->epoch || t->status != sites[0]->status || t->x_stamped != sites[0]->x_stamped) {
+            set_error("fc_decode_tp_batch: site %d is null, malformed, or differs from site 0 in world / epoch / status", i);
+            return Q4FC_EINVAL;
+        }
+        if ((c.x == nullptr) == (c.xq == nullptr) || (c.x && c.x != calls[0].x) || (c.xq && t->x_stamped)) {
+            set_error("fc_decode_tp_batch: call %d: exactly one of x (shared by all calls) and xq must be given", i);
+            return Q4FC_EINVAL;
+        }
+        if (t->col_off < 0 || t->col_off % 32 != 0 || t->col_off + c.N > c.ldy) {
+            set_error("fc_decode_tp_batch: call %d: col_off must be a multiple of 32 with col_off + N <= ldy", i);
+            return Q4FC_EINVAL;
+        }
+        for (int r = 0; r < t->world; r++)
+            if (!t->y_peer[r] || !aligned(t->y_peer[r], 8)) {
+                set_error("fc_decode_tp_batch: call %d: y_peer[%d] is null or not 8-byte aligned", i, r);
+                return Q4FC_EINVAL;
+            }
+        if (c.xq)
+            if (int rc = check_xq_args("fc_decode_tp_batch", c.rows, c.K, group_k, c.xq)) return rc;
+        if (c.x && t->x_stamped && !aligned(c.x, 8)) {
+            set_error("fc_decode_tp_batch: a stamped x needs 8-byte alignment");
+            return Q4FC_EALIGN;
+        }
+        if (int rc = check_fc_args("fc_decode_tp_batch", static_cast<const float*>(c.x ? c.x : c.xq), c.rows, c.K,
+                                   c.x ? c.ldx : c.K, c.wq, c.Ng, c.Kg, qtype, group_k, c.N,
+                                   reinterpret_cast<float*>(t->y_peer[0]), c.ldy))
+            return rc;
+        if (c.rows > kMaxDecodeRows) {
+            set_error("fc_decode_tp_batch: rows=%lld exceeds %d", (long long)c.rows, kMaxDecodeRows);
+            return Q4FC_ELIMIT;
+        }
+    }
+    return launch_fc_decode_ring_tp_batch(calls, sites, ncalls, qtype, group_k, flags, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_tp_collect_multi(const unsigned long long* const* stamped, const int64_t* rows, const int64_t* N,
+                          const int64_t* ld, float* const* dst, const int64_t* ldd, int n,
+                          const unsigned long long* epoch, int* status, q4fc_stream_t stream) {
+    if (!stamped || !rows || !N || !ld || !epoch || !status || n < 1 || n > 16) {
+        set_error("tp_collect_multi: null argument or n=%d outside 1..16", n);
+        return Q4FC_EINVAL;
+    }
+    for (int i = 0; i < n; i++)
+        if (!stamped[i] || !aligned(stamped[i], 8) || rows[i] < 0 || N[i] < 0 || ld[i] < N[i] ||
+            (dst && dst[i] && (!ldd || ldd[i] < N[i]))) {
+            set_error("tp_collect_multi: buffer %d: null or misaligned pointer, negative size, or pitch smaller than N", i);
+            return Q4FC_EINVAL;
+        }
+    return launch_tp_collect_multi(stamped, rows, N, ld, dst, ldd, n, epoch, status, static_cast<cudaStream_t>(stream));
+}
+
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream) {
     if (!ws) {
         ws = ring_status_word();

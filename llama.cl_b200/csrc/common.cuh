@@ -87,6 +87,11 @@ int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, 
 int launch_fc_decode_ring_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                                 int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,
                                 const q4fc_tp_site* tp);
+int launch_fc_decode_ring_tp_batch(const q4fc_tp_call* calls, const q4fc_tp_site* const* sites, int ncalls, int qtype,
+                                   int G, unsigned flags, cudaStream_t s);
+int launch_tp_collect_multi(const unsigned long long* const* src, const int64_t* rows, const int64_t* N,
+                            const int64_t* ld, float* const* dst, const int64_t* ldd, int n,
+                            const unsigned long long* epoch, int* status, cudaStream_t s);
 // step barrier and stream-side wait of the N-split over several GPUs
 int launch_tp_step_begin(unsigned long long* epoch, unsigned long long* const* barrier_peer,
                          const unsigned long long* barrier_local, int world, int* status, cudaStream_t s);

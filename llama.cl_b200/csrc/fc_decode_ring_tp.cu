@@ -77,7 +77,76 @@ __global__ void tp_collect_kernel(const unsigned long long* src, int rows, int64
     }
 }
 
+struct CollectArgs {
+    const unsigned long long* src[16];
+    float* dst[16];
+    int64_t N[16], ld[16], ldd[16];
+    int64_t end[16];  // one past the last word of buffer i in the launch's common index space
+    int n;
+};
+
+// tp_collect_kernel over several buffers; dst == nullptr: only wait for the buffer's words
+__global__ void tp_collect_multi_kernel(const CollectArgs a, const unsigned long long* epoch, int* status) {
+    const uint32_t stamp = (uint32_t)*reinterpret_cast<const volatile unsigned long long*>(epoch);
+    const int64_t total = a.end[a.n - 1];
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int b = 0;
+        while (i >= a.end[b]) b++;
+        const int64_t r = i - (b ? a.end[b - 1] : 0);
+        const int64_t m = r / a.N[b], n = r - m * a.N[b];
+        const unsigned long long* p = a.src[b] + m * a.ld[b] + n;
+        unsigned long long w = ld_stamped(p);
+        if ((uint32_t)(w >> 32) != stamp) {
+            const unsigned long long t0 = globaltimer_ns();
+            for (unsigned it = 1;; it++) {
+                w = ld_stamped(p);
+                if ((uint32_t)(w >> 32) == stamp) break;
+                if ((it & 63) == 0) {
+                    if (*reinterpret_cast<volatile int*>(status) != 0) break;
+                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        atomicCAS(status, 0, 0x54505754);  // 'TPWT'
+                        break;
+                    }
+                }
+            }
+        }
+        if (a.dst[b] != nullptr) a.dst[b][m * a.ldd[b] + n] = __uint_as_float((uint32_t)w);
+    }
+}
+
 }  // namespace
+
+int launch_fc_decode_ring_tp_batch(const q4fc_tp_call* calls, const q4fc_tp_site* const* sites, int ncalls, int qtype,
+                                   int G, unsigned flags, cudaStream_t s) {
+    RingCall c[kMaxTpJobs];
+    for (int i = 0; i < ncalls; i++)
+        c[i] = {static_cast<const float*>(calls[i].x), calls[i].ldx, calls[i].xq, (int)calls[i].rows, calls[i].K,
+                calls[i].Kg, static_cast<const uint8_t*>(calls[i].wq), calls[i].Ng, calls[i].N, nullptr, calls[i].ldy,
+                nullptr, 0};
+    return launch_ring_impl<true>(c, ncalls, qtype, G, flags, s, sites, nullptr, 0);
+}
+
+int launch_tp_collect_multi(const unsigned long long* const* src, const int64_t* rows, const int64_t* N,
+                            const int64_t* ld, float* const* dst, const int64_t* ldd, int n,
+                            const unsigned long long* epoch, int* status, cudaStream_t s) {
+    CollectArgs a = {};
+    int64_t total = 0;
+    int k = 0;
+    for (int i = 0; i < n; i++) {
+        if (rows[i] == 0 || N[i] == 0) continue;
+        a.src[k] = src[i], a.dst[k] = dst ? dst[i] : nullptr, a.N[k] = N[i], a.ld[k] = ld[i];
+        a.ldd[k] = (dst && dst[i]) ? ldd[i] : 0;
+        total += rows[i] * N[i];
+        a.end[k] = total;
+        k++;
+    }
+    if (k == 0) return Q4FC_OK;
+    a.n = k;
+    const int64_t blocks = (total + 255) / 256;
+    tp_collect_multi_kernel<<<(unsigned)(blocks < 1184 ? blocks : 1184), 256, 0, s>>>(a, epoch, status);
+    Q4FC_CUDA_OK(cudaGetLastError());
+    return Q4FC_OK;
+}
 
 int launch_fc_decode_ring_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                              int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,

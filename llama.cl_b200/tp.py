@@ -327,6 +327,18 @@ class FusedTPLinearQ4:
             self._sites[stamped] = s
         return self._sites[stamped]
 
+    def _site_plain(self) -> "_cabi.TpSite":
+        """Site for a plain fp32 input that is quantized inside the kernel (no scratch)."""
+        if "plain" not in self._sites:
+            src = self._site(False)
+            s = _cabi.TpSite()
+            s.world, s.x_stamped, s.col_off = src.world, 0, src.col_off
+            for r in range(self.world):
+                s.y_peer[r] = src.y_peer[r]
+            s.epoch, s.status, s.xq_scratch = src.epoch, src.status, None
+            self._sites["plain"] = s
+        return self._sites["plain"]
+
     def __call__(self, x: "torch.Tensor | StampedOutput") -> StampedOutput:
         import ctypes as C
 
@@ -352,6 +364,111 @@ class FusedTPLinearQ4:
             self.n1 - self.n0, self.ldy, C.byref(self._site(stamped)), self.flags, self.arena._stream()),
             "fc_decode_tp")
         return StampedOutput(self, B, M)
+
+
+def _site_array(sites):
+    import ctypes as C
+
+    return (C.POINTER(_cabi.TpSite) * len(sites))(*[C.pointer(s) for s in sites])
+
+
+class FusedTPBatch:
+    """Up to four fused N-split FCs of one schedule as ONE launch, each on its own pre-quantized input
+    (``q4fc_fc_decode_tp_batch``): the multi-GPU counterpart of ``llmops.FCBatch``.  ``layers``:
+    ``FusedTPLinearQ4`` objects of the same schedule and block type; ``xqs``: one ``QuantizedActivations`` per
+    layer (replicated on every rank).  The argument block is built once; ``run()`` only launches and returns the
+    layers' ``StampedOutput``s."""
+
+    def __init__(self, layers, xqs) -> None:
+        if not 1 <= len(layers) <= 4 or len(xqs) != len(layers):
+            raise RuntimeError("FusedTPBatch: one to four layers, with one quantized input each")
+        self.layers, self.xqs = list(layers), list(xqs)
+        sched = layers[0].schedule
+        self._calls = (_cabi.TpCall * len(layers))()
+        self._sites = []
+        for i, (l, xq) in enumerate(zip(layers, xqs)):
+            if l.schedule is not sched or (l.qtype, l.group_k) != (layers[0].qtype, layers[0].group_k):
+                raise RuntimeError("FusedTPBatch: the layers differ in schedule or block type")
+            if xq.group_k != l.group_k or xq.Kg != l.Kg or xq.rows > l.max_rows:
+                raise RuntimeError(f"FusedTPBatch: input {i} does not fit its layer")
+            c = self._calls[i]
+            c.x, c.xq, c.rows, c.K, c.ldx = None, xq.buf.data_ptr(), xq.rows, xq.K, xq.K
+            c.wq, c.Ng, c.Kg, c.N, c.ldy = l.weight.data_ptr(), l.nb1 - l.nb0, l.Kg, l.n1 - l.n0, l.ldy
+            s = _cabi.TpSite()
+            a = l.arena
+            s.world, s.x_stamped, s.col_off = l.world, 0, l.nb0 * 32
+            for r in range(l.world):
+                s.y_peer[r] = a.bases[r] + l.y_off
+            s.epoch, s.status, s.xq_scratch = a.local + sched.epoch_off, a.local + a.STATUS, None
+            self._sites.append(s)
+        self._site_ptrs = _site_array(self._sites)
+        self.flags = layers[0].flags
+        self.outs = [StampedOutput(l, xq.B, xq.M) for l, xq in zip(layers, xqs)]
+
+    def run(self):
+        l0 = self.layers[0]
+        _cabi.check(_cabi.lib().q4fc_fc_decode_tp_batch(self._calls, self._site_ptrs, len(self.layers), l0.qtype,
+                                                        l0.group_k, self.flags, l0.arena._stream()),
+                    "fc_decode_tp_batch")
+        return self.outs
+
+
+def fused_multi(layers, x):
+    """Several fused N-split FCs on ONE input as one launch (q/k/v, gate/up): ``x`` is a replicated fp32
+    ``[B, M, K]`` tensor or the ``StampedOutput`` of another layer of the same schedule."""
+    if not 1 <= len(layers) <= 4:
+        raise RuntimeError("fused_multi: one to four layers")
+    l0 = layers[0]
+    stamped = isinstance(x, StampedOutput)
+    if stamped:
+        B, M, K = x.shape
+        rows, ldx, xptr = x.rows, x.ld, x.ptr
+    else:
+        B, M, K = x.shape
+        rows = B * M
+        x2 = x.reshape(rows, K)
+        ldx, xptr = (x2.stride(0) if rows > 1 else K), x2.data_ptr()
+    calls = (_cabi.TpCall * len(layers))()
+    sites = []
+    for i, l in enumerate(layers):
+        if l.schedule is not l0.schedule or (l.qtype, l.group_k, l.Kg) != (l0.qtype, l0.group_k, l0.Kg):
+            raise RuntimeError("fused_multi: the layers differ in schedule, block type or K")
+        c = calls[i]
+        c.x, c.xq, c.rows, c.K, c.ldx = xptr, None, rows, K, ldx
+        c.wq, c.Ng, c.Kg, c.N, c.ldy = l.weight.data_ptr(), l.nb1 - l.nb0, l.Kg, l.n1 - l.n0, l.ldy
+        s = l._site(stamped)
+        if not stamped and s.xq_scratch:
+            s = l._site_plain()
+        sites.append(s)
+    _cabi.check(_cabi.lib().q4fc_fc_decode_tp_batch(calls, _site_array(sites), len(layers), l0.qtype, l0.group_k,
+                                                    l0.flags, l0.arena._stream()), "fc_decode_tp_batch")
+    return [StampedOutput(l, B, M) for l in layers]
+
+
+def collect_many(outs, dsts=None) -> None:
+    """``StampedOutput.tensor`` for up to 16 outputs of one schedule in ONE launch (``q4fc_tp_collect_multi``).
+    ``dsts[i]``: contiguous fp32 ``[B, M, N]`` tensor, or None to only wait until output i is complete."""
+    import ctypes as C
+
+    n = len(outs)
+    if not 1 <= n <= 16:
+        raise RuntimeError("collect_many: one to sixteen outputs")
+    a = outs[0].layer.arena
+    sched = outs[0].layer.schedule
+    i64 = C.c_int64
+    src = (C.c_void_p * n)(*[o.ptr for o in outs])
+    rows = (i64 * n)(*[o.rows for o in outs])
+    N = (i64 * n)(*[o.N for o in outs])
+    ld = (i64 * n)(*[o.ld for o in outs])
+    dst = (C.c_void_p * n)(*[(d.data_ptr() if d is not None else None) for d in (dsts or [None] * n)])
+    ldd = (i64 * n)(*[o.N for o in outs])
+    for o, d in zip(outs, dsts or []):
+        if o.layer.schedule is not sched:
+            raise RuntimeError("collect_many: the outputs belong to different schedules")
+        if d is not None and (d.shape != o.shape or d.dtype != torch.float32 or not d.is_contiguous()):
+            raise RuntimeError("collect_many: every dst must be a contiguous fp32 [B, M, N] tensor")
+    _cabi.check(_cabi.lib().q4fc_tp_collect_multi(src, rows, N, ld, dst, ldd, n, a.local + sched.epoch_off,
+                                                  a.local + a.STATUS, a._stream()), "tp_collect_multi")
 
 
 class HostFusedFC:
@@ -412,3 +529,110 @@ class HostFusedFC:
             self.stream.synchronize()
             self.layer.arena.check()  # a bounded wait on another rank that ran out makes the result invalid
         return self._y_host[:, :M]
+
+
+class HostFusedBatch:
+    """``host.HostFCBatch`` over N-split weights: a fixed batch of independent host-buffer FCs with one copy each
+    way per step.  Every rank makes the same call with the same activations.  ``members``: ``(wq_shard, N, rows)``.
+    Per step: one host-to-device copy of all inputs, the quantizers, the step barrier, one
+    ``q4fc_fc_decode_tp_batch`` launch per group of up to four members of one row count, one unpacking launch
+    into the common output block, one device-to-host copy -- captured once as a CUDA graph and replayed."""
+
+    def __init__(self, arena: TPArena, members, *, graph: bool = True) -> None:
+        from . import llmops
+
+        self.arena = arena
+        self.schedule = TPSchedule(arena)
+        self.members = [(wq, int(N), int(rows)) for wq, N, rows in members]
+        dev = arena.device
+        self.device = dev
+        self.stream = torch.cuda.Stream(dev)
+        self.side = torch.cuda.Stream(dev)
+        self.layers = [FusedTPLinearQ4(self.schedule, wq, N, max_rows=rows, pdl=True) for wq, N, rows in self.members]
+        shapes = [(rows, l.Kg * l.group_k, N, l.group_k) for (wq, N, rows), l in zip(self.members, self.layers)]
+        self._shapes = shapes
+        nx = sum(r * K for r, K, _, _ in shapes)
+        ny = sum(r * N for r, _, N, _ in shapes)
+        self._x_host = torch.empty(nx, dtype=torch.float32).pin_memory()
+        self._y_host = torch.empty(ny, dtype=torch.float32).pin_memory()
+        self._x_dev = torch.empty(nx, dtype=torch.float32, device=dev)
+        self._y_dev = torch.empty(ny, dtype=torch.float32, device=dev)
+        self._xs_host, self._ys_host, self._xs_dev, self._ys_dev = [], [], [], []
+        ox = oy = 0
+        for r, K, N, _ in shapes:
+            self._xs_host.append(self._x_host[ox: ox + r * K].view(1, r, K))
+            self._xs_dev.append(self._x_dev[ox: ox + r * K].view(1, r, K))
+            self._ys_host.append(self._y_host[oy: oy + r * N].view(1, r, N))
+            self._ys_dev.append(self._y_dev[oy: oy + r * N].view(1, r, N))
+            ox, oy = ox + r * K, oy + r * N
+        self._xq = [llmops.QuantizedActivations(1, r, K, G, False, dev) for r, K, _, G in shapes]
+        by_rows: dict = {}
+        for i, (r, _, _, _) in enumerate(shapes):
+            by_rows.setdefault(r, []).append(i)
+        self._batches = []
+        for _, idx in sorted(by_rows.items()):
+            for j in range(0, len(idx), 4):
+                part = idx[j: j + 4]
+                self._batches.append((part, FusedTPBatch([self.layers[i] for i in part], [self._xq[i] for i in part])))
+        self.use_graph = bool(graph)
+        self._graph = None
+
+    def x_staging(self, i: int) -> torch.Tensor:
+        return self._xs_host[i]
+
+    def _enqueue(self) -> None:
+        from . import llmops
+
+        cur = torch.cuda.current_stream(self.device)
+        self._x_dev.copy_(self._x_host, non_blocking=True)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        self.side.wait_event(ready)
+        done = []
+        with torch.cuda.stream(self.side):
+            for part, _ in self._batches:
+                for i in part:
+                    llmops.quantize_activations(self._xs_dev[i], self._shapes[i][3], out=self._xq[i])
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                done.append(ev)
+        self.schedule.step_begin()
+        outs, dsts = [], []
+        for (part, fb), ev in zip(self._batches, done):
+            cur.wait_event(ev)
+            outs += fb.run()
+            dsts += [self._ys_dev[i] for i in part]
+        for j in range(0, len(outs), 16):
+            collect_many(outs[j: j + 16], dsts[j: j + 16])
+        self._y_host.copy_(self._y_dev, non_blocking=True)
+
+    def __call__(self, xs=None, sync: bool = True, check: bool = True):
+        """``check`` (with ``sync``): read the status word after the step and raise if a bounded wait on another
+        rank ran out; a caller that checks ``arena.check()`` itself at a coarser grain passes False."""
+        if xs is not None:
+            for x, stage in zip(xs, self._xs_host):
+                if x.data_ptr() != stage.data_ptr():
+                    stage.copy_(x)
+        with torch.cuda.stream(self.stream):
+            if not self.use_graph:
+                self._enqueue()
+            else:
+                if self._graph is None:
+                    self._enqueue()  # eager once (every rank does: the step barrier pairs up), then capture
+                    torch.cuda.synchronize(self.device)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        self._enqueue()
+                    self._graph = g
+                self._graph.replay()
+        if sync:
+            self.stream.synchronize()
+            if check:
+                self.arena.check()  # a bounded wait on another rank that ran out makes the results invalid
+        return self._ys_host
+
+    def h2d_bytes(self) -> int:
+        return self._x_host.numel() * 4
+
+    def d2h_bytes(self) -> int:
+        return self._y_host.numel() * 4

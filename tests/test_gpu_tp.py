@@ -182,6 +182,37 @@ def _fused_worker(rank, world, initfile, result_q):
             torch.cuda.synchronize()
             expect(torch.allclose(ya, yb, rtol=1e-4, atol=1e-5), f"prequant layer M={M}")
 
+        # several layers per launch: q and k on one (stamped or plain) input, and a batch on pre-quantized inputs,
+        # gathered by one unpacking launch
+        sm = tp.TPSchedule(arena)
+        lq = tp.FusedTPLinearQ4(sm, tp.shard_packed(full["q"], world, rank), H, pdl=True)
+        lk = tp.FusedTPLinearQ4(sm, tp.shard_packed(full["k"], world, rank), H, pdl=True)
+        lu = tp.FusedTPLinearQ4(sm, tp.shard_packed(full["up"], world, rank), I, pdl=True)
+        for M in (1, 3):
+            g = torch.Generator().manual_seed(700 + M)
+            xm = torch.randn(1, M, H, generator=g).to(dev)
+            sm.step_begin()
+            oq, ok_ = tp.fused_multi([lq, lk], xm)
+            (ou,) = tp.fused_multi([lu], oq)  # reads the stamped output of q
+            yq, yk, yu = (torch.empty((1, M, n), device=dev) for n in (H, H, I))
+            tp.collect_many([oq, ok_, ou], [yq, yk, yu])
+            torch.cuda.synchronize()
+            for name, y, xin in (("q", yq, xm), ("k", yk, xm), ("up", yu, yq)):
+                ref = torch.from_numpy(cpu.restated.fc(xin.cpu().numpy(), full_np[name], y.shape[-1])).to(dev)
+                expect(torch.allclose(y, ref, rtol=1e-3, atol=1e-4), f"fused_multi {name} M={M}: differs from the oracle")
+        xqa = pkg.llmops.quantize_activations(torch.randn(1, 2, H, generator=torch.Generator().manual_seed(801)).to(dev), 128)
+        xqb = pkg.llmops.quantize_activations(torch.randn(1, 2, H, generator=torch.Generator().manual_seed(802)).to(dev), 128)
+        fb = tp.FusedTPBatch([lq, lu], [xqa, xqb])
+        for step in range(2):
+            sm.step_begin()
+            outs_b = fb.run()
+            ya, yb = torch.empty((1, 2, H), device=dev), torch.empty((1, 2, I), device=dev)
+            tp.collect_many(outs_b, [ya, yb])
+            torch.cuda.synchronize()
+            expect(torch.allclose(ya, pkg.llmops.fc_Q4A_q8(xqa, full["q"], H), rtol=1e-3, atol=1e-4), f"FusedTPBatch q step {step}")
+            expect(torch.allclose(yb, pkg.llmops.fc_Q4A_q8(xqb, full["up"], I), rtol=1e-3, atol=1e-4), f"FusedTPBatch up step {step}")
+        expect(arena.status() == 0, f"status {arena.status():#x} after the batched launches")
+
         # host buffers in and out over the N-split FC, as a replayed graph, two row counts, fresh inputs
         hf = tp.HostFusedFC(arena, tp.shard_packed(full["up"], world, rank), I, max_rows=4, pdl=True)
         for step in range(3):
