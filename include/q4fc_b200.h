@@ -319,10 +319,40 @@ int q4fc_tp_collect_multi(const unsigned long long* const* stamped, const int64_
                           const int64_t* ld, float* const* dst, const int64_t* ldd, int n,
                           const unsigned long long* epoch, int* status, q4fc_stream_t stream);
 
+/* ---- per-channel int8 weights ("Q8C"): the FC of the reference's older extension and its embedding table ------
+ *
+ *   q4fc_q8c_pack         replaces FC_quant_Q8C (ext/llama_ext.cpp:56-113).  w: fp32 row-major [N][K] on the device.
+ *                         wq: int8 [Ng][Kg][1024] (Ng = ceil(N/32), Kg = ceil(K/32); q8_c_block,
+ *                         ext/llama_ext.cpp:50-54), wscales: fp32 [Ng*32].  Bit-identical to the reference.
+ *   q4fc_q8c_workspace_bytes / q4fc_q8c_fc
+ *                         replace FC_evaluate_Q8C (ext/llama_ext.cpp:232-371): the activations are quantized per
+ *                         32-group with scale 1 and no group sums (its FC_dynamic_quantize_x call, :360) into the
+ *                         workspace, then y[m][n] = wscales[n] * sum over groups of dx[m][kb] * (codes . q).  The
+ *                         integer sums are exact; the fp32 sum over groups is split over warps (and CTAs of a
+ *                         cluster), so y agrees with the reference within fp32 rounding (1e-3 relative / 1e-4
+ *                         absolute is the tested bound), the same from run to run.  Any rows >= 0; N need not be a
+ *                         multiple of 32 (the reference stores whole 32-column groups and overruns its output
+ *                         there).  ws: device scratch of q4fc_q8c_workspace_bytes(rows, K) bytes, 256-byte aligned.
+ *   q4fc_emb_q8c_quant    replaces embedding_q8c_quant_w (ops/op_embedding.hpp:51-78): per row of the fp32 table
+ *                         [V][E] one scale amax/127 and int8 codes [V][E].  Bit-identical to the reference.
+ *   q4fc_emb_q8c          replaces embedding_q8c (ops/op_embedding.hpp:80-137): out[i][:] = scales[id] * codes[id][:]
+ *                         for n ids (int64, or int32 when ids_are_i32 != 0) on the device; out fp32 [n][ldo].
+ *                         Bit-identical.  The reference does not check the ids; here an id outside [0, V) gives a
+ *                         row of zeros and sets the device status word that q4fc_fc_check_status(NULL, ..) reads. */
+int q4fc_q8c_pack(const float* w, int64_t N, int64_t K, int8_t* wq, float* wscales, q4fc_stream_t stream);
+size_t q4fc_q8c_workspace_bytes(int64_t rows, int64_t K);
+int q4fc_q8c_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const int8_t* wq, const float* wscales,
+                int64_t Ng, int64_t Kg, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
+                q4fc_stream_t stream);
+int q4fc_emb_q8c_quant(const float* table, int64_t V, int64_t E, int8_t* codes, float* scales, q4fc_stream_t stream);
+int q4fc_emb_q8c(const void* ids, int ids_are_i32, int64_t n, const int8_t* codes, const float* scales, int64_t V,
+                 int64_t E, float* out, int64_t ldo, q4fc_stream_t stream);
+
 /* Reads and clears the device status word kept at the start of a workspace
  * (host-synchronous: waits for `stream`).  ws = NULL reads the word that decode
  * calls made without a workspace share (one per device).  Returns Q4FC_OK or
- * Q4FC_EDEVICE (a bounded wait inside a kernel ran out; its results are invalid). */
+ * Q4FC_EDEVICE (a bounded wait inside a kernel ran out, or an embedding id was out of range; the results
+ * are invalid). */
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream);
 
 #if defined(__GNUC__)

@@ -28,6 +28,7 @@ SYMBOLS = (
     "q4fc_fc_decode_tp_batch", "q4fc_tp_collect_multi",
     "q4fc_xq_bytes", "q4fc_quant_x_q8", "q4fc_rmsnorm_quant", "q4fc_add_rmsnorm_quant", "q4fc_fc_decode_q8",
     "q4fc_silu_mul_quant",
+    "q4fc_q8c_pack", "q4fc_q8c_workspace_bytes", "q4fc_q8c_fc", "q4fc_emb_q8c_quant", "q4fc_emb_q8c",
 )
 
 
@@ -131,6 +132,12 @@ def lib() -> C.CDLL:
     L.q4fc_add_rmsnorm_quant.argtypes = [vp, vp, vp, i64, i64, i64, vp, f32, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_silu_mul_quant.argtypes = [vp, vp, i64, i64, i64, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_fc_decode_q8.argtypes = [vp, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, u32, vp]
+    L.q4fc_q8c_pack.argtypes = [vp, i64, i64, vp, vp, vp]
+    L.q4fc_q8c_workspace_bytes.restype = sz
+    L.q4fc_q8c_workspace_bytes.argtypes = [i64, i64]
+    L.q4fc_q8c_fc.argtypes = [vp, i64, i64, i64, vp, vp, i64, i64, i64, vp, i64, vp, sz, vp]
+    L.q4fc_emb_q8c_quant.argtypes = [vp, i64, i64, vp, vp, vp]
+    L.q4fc_emb_q8c.argtypes = [vp, i32, i64, vp, vp, i64, i64, vp, i64, vp]
     L.q4fc_tp_site_bytes.restype = sz
     if L.q4fc_tp_site_bytes() != C.sizeof(TpSite):
         raise RuntimeError(f"q4fc_tp_site is {L.q4fc_tp_site_bytes()} bytes in the library, {C.sizeof(TpSite)} here")

@@ -640,6 +640,96 @@ int q4fc_tp_collect_multi(const unsigned long long* const* stamped, const int64_
     return launch_tp_collect_multi(stamped, rows, N, ld, dst, ldd, n, epoch, status, static_cast<cudaStream_t>(stream));
 }
 
+int q4fc_q8c_pack(const float* w, int64_t N, int64_t K, int8_t* wq, float* wscales, q4fc_stream_t stream) {
+    if (N < 0 || K < 0) {
+        set_error("q8c_pack: negative size");
+        return Q4FC_EINVAL;
+    }
+    if (N == 0) return Q4FC_OK;
+    if (!w || !wq || !wscales) {
+        set_error("q8c_pack: null pointer");
+        return Q4FC_EINVAL;
+    }
+    if (!aligned(wq, 4)) {
+        set_error("q8c_pack: wq needs 4-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    return launch_q8c_pack(w, N, K, wq, wscales, static_cast<cudaStream_t>(stream));
+}
+
+size_t q4fc_q8c_workspace_bytes(int64_t rows, int64_t K) {
+    if (rows < 0 || K < 0) return 0;
+    return q8c_workspace_bytes(rows, K);
+}
+
+int q4fc_q8c_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const int8_t* wq, const float* wscales,
+                int64_t Ng, int64_t Kg, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,
+                q4fc_stream_t stream) {
+    if (rows < 0 || K < 0 || N < 0 || Ng < 0 || Kg < 0) {
+        set_error("q8c_fc: negative size");
+        return Q4FC_EINVAL;
+    }
+    if (Kg != (K + 31) / 32 || N > Ng * 32) {
+        set_error("q8c_fc: weights [%lld][%lld][1024] do not match K=%lld, N=%lld", (long long)Ng, (long long)Kg,
+                  (long long)K, (long long)N);
+        return Q4FC_EINVAL;
+    }
+    if (rows == 0 || N == 0) return Q4FC_OK;
+    if (!y || !wscales || (K > 0 && (!x || !wq))) {
+        set_error("q8c_fc: null pointer");
+        return Q4FC_EINVAL;
+    }
+    if (ldx < K || ldy < N) {
+        set_error("q8c_fc: ldx=%lld / ldy=%lld smaller than K=%lld / N=%lld", (long long)ldx, (long long)ldy,
+                  (long long)K, (long long)N);
+        return Q4FC_EINVAL;
+    }
+    if (!aligned(wq, 16) || !aligned(x, 4)) {
+        set_error("q8c_fc: wq needs 16-byte and x 4-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    if (K > 0 && (!ws || ws_bytes < q8c_workspace_bytes(rows, K))) {
+        set_error("q8c_fc: workspace of %zu bytes, need %zu", ws ? ws_bytes : (size_t)0, q8c_workspace_bytes(rows, K));
+        return Q4FC_EWORKSPACE;
+    }
+    if (ws && !aligned(ws, 256)) {
+        set_error("q8c_fc: workspace needs 256-byte alignment");
+        return Q4FC_EALIGN;
+    }
+    return launch_q8c_fc(x, rows, K, ldx, wq, wscales, Ng, Kg, N, y, ldy, ws, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_emb_q8c_quant(const float* table, int64_t V, int64_t E, int8_t* codes, float* scales, q4fc_stream_t stream) {
+    if (V < 0 || E < 0) {
+        set_error("emb_q8c_quant: negative size");
+        return Q4FC_EINVAL;
+    }
+    if (V == 0) return Q4FC_OK;
+    if (!scales || (E > 0 && (!table || !codes))) {
+        set_error("emb_q8c_quant: null pointer");
+        return Q4FC_EINVAL;
+    }
+    return launch_emb_q8c_quant(table, V, E, codes, scales, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_emb_q8c(const void* ids, int ids_are_i32, int64_t n, const int8_t* codes, const float* scales, int64_t V,
+                 int64_t E, float* out, int64_t ldo, q4fc_stream_t stream) {
+    if (n < 0 || V < 0 || E < 0) {
+        set_error("emb_q8c: negative size");
+        return Q4FC_EINVAL;
+    }
+    if (n == 0 || E == 0) return Q4FC_OK;
+    if (!ids || !codes || !scales || !out) {
+        set_error("emb_q8c: null pointer");
+        return Q4FC_EINVAL;
+    }
+    if (ldo < E) {
+        set_error("emb_q8c: ldo=%lld smaller than E=%lld", (long long)ldo, (long long)E);
+        return Q4FC_EINVAL;
+    }
+    return launch_emb_q8c(ids, ids_are_i32, n, codes, scales, V, E, out, ldo, static_cast<cudaStream_t>(stream));
+}
+
 int q4fc_fc_check_status(void* ws, q4fc_stream_t stream) {
     if (!ws) {
         ws = ring_status_word();
@@ -651,7 +741,8 @@ int q4fc_fc_check_status(void* ws, q4fc_stream_t stream) {
     Q4FC_CUDA_OK(cudaStreamSynchronize(s));
     if (status != 0) {
         Q4FC_CUDA_OK(cudaMemsetAsync(ws, 0, sizeof(int), s));
-        set_error("device status word = 0x%x (a bounded wait ran out)", status);
+        set_error("device status word = 0x%x (%s)", status,
+                  (status & 0x100) ? "an embedding id was out of range" : "a bounded wait ran out");
         return Q4FC_EDEVICE;
     }
     return Q4FC_OK;

@@ -97,6 +97,14 @@ int launch_tp_step_begin(unsigned long long* epoch, unsigned long long* const* b
                          const unsigned long long* barrier_local, int world, int* status, cudaStream_t s);
 int launch_tp_collect(const unsigned long long* src, int64_t rows, int64_t N, int64_t ld, float* dst, int64_t ldd,
                       const unsigned long long* epoch, int* status, cudaStream_t s);
+// per-channel int8 weights and the quantized embedding table (q8c.cu)
+int launch_q8c_pack(const float* w, int64_t N, int64_t K, int8_t* wq, float* wscales, cudaStream_t s);
+size_t q8c_workspace_bytes(int64_t rows, int64_t K);
+int launch_q8c_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const int8_t* wq, const float* wscales,
+                  int64_t Ng, int64_t Kg, int64_t N, float* y, int64_t ldy, void* ws, cudaStream_t s);
+int launch_emb_q8c_quant(const float* table, int64_t V, int64_t E, int8_t* codes, float* scales, cudaStream_t s);
+int launch_emb_q8c(const void* ids, int ids_are_i32, int64_t n, const int8_t* codes, const float* scales, int64_t V,
+                   int64_t E, float* out, int64_t ldo, cudaStream_t s);
 size_t prefill_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int G);
 int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                       int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,

@@ -24,7 +24,7 @@ from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, FLAG_STREAMK, Q4_0, Q4_1
 
 __all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
            "fc_workspace", "Workspace", "fc_Q4A_multi", "FCBatch", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize", "silu_mul_quantize",
-           "QuantizedActivations"]
+           "QuantizedActivations", "FC_quant_Q8C", "FC_evaluate_Q8C", "embedding_q8c_quant_w", "embedding_q8c", "check_device_status"]
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -465,6 +465,104 @@ class FCBatch:
             _cabi.check(_cabi.lib().q4fc_fc_decode_batch(self._args, self.n, self.qtype, self.group_k, self.flags,
                                                          _stream_ptr(self.device)), "fc_decode_batch")
         return self.outs
+
+
+# ---- per-channel int8 weights ("Q8C") and the quantized embedding table ---------------------------------------------
+_q8c_scratch: dict = {}
+
+
+def FC_quant_Q8C(wei: torch.Tensor):
+    """fp32 ``[N, K]`` -> (int8 ``[ceil(N/32), ceil(K/32), 1024]``, fp32 scales ``[ceil(N/32)*32]``), bit-identical to
+    ``FC_quant_Q8C`` of the reference's older extension (ext/llama_ext.cpp:56-113)."""
+    _require_cuda(wei, "wei", torch.float32, 2)
+    N, K = wei.shape
+    Ng, Kg = (N + 31) // 32, (K + 31) // 32
+    wq = torch.empty((Ng, Kg, 1024), dtype=torch.int8, device=wei.device)
+    ws = torch.empty((Ng * 32,), dtype=torch.float32, device=wei.device)
+    with torch.cuda.device(wei.device):
+        _cabi.check(_cabi.lib().q4fc_q8c_pack(wei.data_ptr(), N, K, wq.data_ptr(), ws.data_ptr(),
+                                              _stream_ptr(wei.device)), "FC_quant_Q8C")
+    return wq, ws
+
+
+def FC_evaluate_Q8C(input: torch.Tensor, wei_quantized: torch.Tensor, wei_scales: torch.Tensor, N: int, *,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """``[B, M, K]`` x Q8C weights -> ``[B, M, N]`` (ext/llama_ext.cpp:336-371).  The scratch for the quantized
+    activations is kept per (device, stream) and grows to the largest call; calls on one stream are ordered."""
+    _require_cuda(input, "input", torch.float32, 3)
+    _require_cuda(wei_quantized, "wei_quantized", torch.int8, 3)
+    _require_cuda(wei_scales, "wei_scales", torch.float32, 1)
+    B, M, K = input.shape
+    Ng, Kg, bs = wei_quantized.shape
+    if bs != 1024:
+        raise RuntimeError(f"assert wei_quantized.size(2) == sizeof(q8_c_block) failed: got {bs}")
+    if Kg != (K + 31) // 32 or N > Ng * 32 or wei_scales.numel() < N:
+        raise RuntimeError(f"FC_evaluate_Q8C: weights {tuple(wei_quantized.shape)} / scales {tuple(wei_scales.shape)} "
+                           f"do not match K={K}, N={N}")
+    dev = input.device
+    if out is None:
+        out = torch.empty((B, M, N), dtype=torch.float32, device=dev)
+    else:
+        _require_cuda(out, "out", torch.float32, 3)
+        if tuple(out.shape) != (B, M, N):
+            raise RuntimeError(f"out: expected shape {(B, M, N)}, got {tuple(out.shape)}")
+    L = _cabi.lib()
+    need = L.q4fc_q8c_workspace_bytes(B * M, K)
+    with torch.cuda.device(dev):
+        stream = _stream_ptr(dev)
+        key = (dev.index, stream)
+        ws = _q8c_scratch.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(max(need, 1 << 16), dtype=torch.uint8, device=dev)
+            _q8c_scratch[key] = ws
+        _cabi.check(L.q4fc_q8c_fc(input.data_ptr(), B * M, K, K, wei_quantized.data_ptr(), wei_scales.data_ptr(), Ng,
+                                  Kg, N, out.data_ptr(), N, ws.data_ptr(), ws.numel(), stream), "FC_evaluate_Q8C")
+    return out
+
+
+def embedding_q8c_quant_w(weight: torch.Tensor):
+    """fp32 table ``[V, E]`` -> (int8 codes ``[V, E]``, fp32 scales ``[V]``), bit-identical to the reference's
+    ``llmops.embedding_q8c_quant_w`` (ops/op_embedding.hpp:51-78)."""
+    _require_cuda(weight, "weight", torch.float32, 2)
+    V, E = weight.shape
+    codes = torch.empty((V, E), dtype=torch.int8, device=weight.device)
+    scales = torch.empty((V,), dtype=torch.float32, device=weight.device)
+    with torch.cuda.device(weight.device):
+        _cabi.check(_cabi.lib().q4fc_emb_q8c_quant(weight.data_ptr(), V, E, codes.data_ptr(), scales.data_ptr(),
+                                                   _stream_ptr(weight.device)), "embedding_q8c_quant_w")
+    return codes, scales
+
+
+def embedding_q8c(output: torch.Tensor, input: torch.Tensor, weight: torch.Tensor, scales: torch.Tensor) -> None:
+    """``output[..., :] = scales[id] * weight[id, :]`` for the ids in ``input`` (int32 or int64, any rank), with the
+    reference's argument order and in-place result (ops/op_embedding.hpp:108-137).  An id outside the table gives a
+    row of zeros and makes ``check_device_status`` raise."""
+    _require_cuda(weight, "weight", torch.int8, 2)
+    _require_cuda(scales, "scales", torch.float32, 1)
+    if not isinstance(input, torch.Tensor) or input.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("assert input.is<int64_t>() failed: ids must be int32 or int64")
+    if not input.is_cuda or not input.is_contiguous():
+        raise RuntimeError("input: must be a contiguous CUDA tensor")
+    V, E = weight.shape
+    if not isinstance(output, torch.Tensor) or output.dtype != torch.float32:
+        raise RuntimeError("assert output.is<float>() failed")
+    if tuple(output.shape) != tuple(input.shape) + (E,):
+        raise RuntimeError(f"assert infer_shape() == output.shape() failed: {tuple(output.shape)} vs "
+                           f"{tuple(input.shape) + (E,)}")
+    if not output.is_cuda or not output.is_contiguous():
+        raise RuntimeError("output: must be a contiguous CUDA tensor")
+    with torch.cuda.device(weight.device):
+        _cabi.check(_cabi.lib().q4fc_emb_q8c(input.data_ptr(), int(input.dtype == torch.int32), input.numel(),
+                                             weight.data_ptr(), scales.data_ptr(), V, E, output.data_ptr(), E,
+                                             _stream_ptr(weight.device)), "embedding_q8c")
+
+
+def check_device_status(device: torch.device | None = None) -> None:
+    """Raises if a kernel launched without a workspace on this device reported a failure (a bounded wait that ran
+    out, an embedding id outside its table).  Host-synchronous on the current stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _cabi.check(_cabi.lib().q4fc_fc_check_status(None, _stream_ptr(dev)), "check_device_status")
 
 
 def fc_Q4A2(input, wei_quantized, N):

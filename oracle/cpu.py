@@ -64,6 +64,10 @@ class _Restated:
             lib.oracle_fc.argtypes = [fp, i64, i64, u8p, i64, i64, i32, i32, i64, i32, fp, i64]
             lib.oracle_rmsnorm.argtypes = [fp, i64, i64, fp, f32]
             lib.oracle_silu_mul.argtypes = [fp, fp, i64, fp]
+            lib.oracle_q8c_pack.argtypes = [fp, i64, i64, i8p, fp]
+            lib.oracle_q8c_fc.argtypes = [fp, i64, i64, i8p, fp, i64, i64, i64, fp, i64]
+            lib.oracle_emb_q8c_quant.argtypes = [fp, i64, i64, i8p, fp]
+            lib.oracle_emb_q8c.argtypes = [C.POINTER(C.c_int64), i64, i8p, fp, i64, fp]
             lib.oracle_f32_to_f16.argtypes = [f32]
             lib.oracle_f32_to_f16.restype = C.c_uint16
             lib.oracle_f16_to_f32.argtypes = [C.c_uint16]
@@ -141,6 +145,54 @@ class _Restated:
         rc = self.lib.oracle_silu_mul(_p(g, C.c_float), _p(u, C.c_float), g.size, _p(out, C.c_float))
         if rc:
             raise RuntimeError(f"oracle_silu_mul failed ({rc})")
+        return out
+
+    def q8c_pack(self, w):
+        """FC_quant_Q8C (ext/llama_ext.cpp:56-113): -> (int8 [Ng][Kg][1024], fp32 scales [Ng*32])."""
+        w = _f32(w)
+        N, K = w.shape
+        Ng, Kg = (N + 31) // 32, (K + 31) // 32
+        wq = np.empty((Ng, Kg, 1024), dtype=np.int8)
+        sc = np.empty((Ng * 32,), dtype=np.float32)
+        if self.lib.oracle_q8c_pack(_p(w, C.c_float), N, K, _p(wq, C.c_int8), _p(sc, C.c_float)):
+            raise RuntimeError("oracle_q8c_pack failed")
+        return wq, sc
+
+    def q8c_fc(self, x, wq, wscales, N: int) -> np.ndarray:
+        """FC_evaluate_Q8C (ext/llama_ext.cpp:232-371)."""
+        x = _f32(x)
+        wq = np.ascontiguousarray(wq, dtype=np.int8)
+        ws = _f32(wscales)
+        Ng, Kg, _ = wq.shape
+        K = x.shape[-1]
+        rows = x.size // K
+        y = np.zeros(x.shape[:-1] + (N,), dtype=np.float32)
+        rc = self.lib.oracle_q8c_fc(_p(x, C.c_float), rows, K, _p(wq, C.c_int8), _p(ws, C.c_float), Ng, Kg, N,
+                                    _p(y, C.c_float), N)
+        if rc:
+            raise RuntimeError(f"oracle_q8c_fc failed ({rc})")
+        return y
+
+    def emb_q8c_quant(self, w):
+        """embedding_q8c_quant_w (ops/op_embedding.hpp:51-78): -> (int8 [V][E], fp32 scales [V])."""
+        w = _f32(w)
+        V, E = w.shape
+        codes = np.empty((V, E), dtype=np.int8)
+        sc = np.empty((V,), dtype=np.float32)
+        if self.lib.oracle_emb_q8c_quant(_p(w, C.c_float), V, E, _p(codes, C.c_int8), _p(sc, C.c_float)):
+            raise RuntimeError("oracle_emb_q8c_quant failed")
+        return codes, sc
+
+    def emb_q8c(self, ids, codes, scales) -> np.ndarray:
+        """embedding_q8c (ops/op_embedding.hpp:80-137)."""
+        ids = np.ascontiguousarray(ids, dtype=np.int64)
+        codes = np.ascontiguousarray(codes, dtype=np.int8)
+        sc = _f32(scales)
+        E = codes.shape[1]
+        out = np.empty(ids.shape + (E,), dtype=np.float32)
+        if self.lib.oracle_emb_q8c(_p(ids, C.c_int64), ids.size, _p(codes, C.c_int8), _p(sc, C.c_float), E,
+                                   _p(out, C.c_float)):
+            raise RuntimeError("oracle_emb_q8c failed")
         return out
 
     def f16_bits(self, v: float) -> int:

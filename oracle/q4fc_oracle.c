@@ -395,6 +395,88 @@ int oracle_silu_mul(const float* gate, const float* up, int64_t n, float* out) {
     return 0;
 }
 
+/* ---- per-channel int8 weights ("Q8C") of the older extension ----------------------------------------------
+ * FC_quant_Q8C (ext/llama_ext.cpp:56-113): per output column n, amax over the whole row of W, d = amax / 127,
+ * q = roundf(w / d) (half away from zero); blocks of 32 columns x 32 k, byte (k >> 2) * 128 + n * 4 + (k & 3)
+ * (q8_c_block, ext/llama_ext.cpp:50-54); columns n >= N and k >= K are zero.  wq: int8 [Ng][Kg][1024],
+ * scales: fp32 [Ng * 32]. */
+int oracle_q8c_pack(const float* w, int64_t N, int64_t K, int8_t* wq, float* scales) {
+    const int64_t Ng = (N + 31) / 32, Kg = (K + 31) / 32;
+    memset(wq, 0, (size_t)(Ng * Kg * 1024));
+    for (int64_t n = 0; n < Ng * 32; n++) {
+        if (n >= N) {
+            scales[n] = 0.0f;
+            continue;
+        }
+        const float* src = w + n * K;
+        float amax = 0.0f;
+        for (int64_t k = 0; k < K; k++) {
+            const float a = fabsf(src[k]);
+            if (amax < a) amax = a;
+        }
+        const float d = amax / 127;
+        const float id = (d != 0) ? (1.0f / d) : 0;
+        scales[n] = d;
+        int8_t* blk = wq + (n / 32) * Kg * 1024;
+        const int noff = (int)(n % 32);
+        for (int64_t k = 0; k < K; k++) {
+            const int ki = (int)(k % 32);
+            blk[(k / 32) * 1024 + (ki >> 2) * 128 + noff * 4 + (ki & 3)] = (int8_t)roundf(src[k] * id);
+        }
+    }
+    return 0;
+}
+
+/* FC_evaluate_Q8C (ext/llama_ext.cpp:232-371): the activations are quantized per 32-group with scale 1 and no
+ * group sums (FC_dynamic_quantize_x, :116-166); per (row, column) the groups in order:
+ *   I = sum_k code(r,k) * q(n,k)  exact (the sign/maddubs form of :289-307 cannot saturate: |code| <= 127),
+ *   acc = fmaf(dx[kb], (float)I, acc);   y = d_w[n] * acc  (:326-333). */
+int oracle_q8c_fc(const float* x, int64_t rows, int64_t K, const int8_t* wq, const float* wscales, int64_t Ng,
+                  int64_t Kg, int64_t N, float* y, int64_t ldy) {
+    if ((K + 31) / 32 != Kg || N > Ng * 32) return 1;
+    int8_t* codes = (int8_t*)malloc((size_t)(rows * Kg * 32 + 1));
+    float* xs = (float*)malloc(sizeof(float) * (size_t)(rows * Kg + 1));
+    if (!codes || !xs) return 2;
+    oracle_quant_x(x, rows, K, 32, 1.0f, codes, xs, NULL);
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; n++) {
+        const int8_t* blk = wq + (n / 32) * Kg * 1024;
+        const int noff = (int)(n % 32);
+        for (int64_t r = 0; r < rows; r++) {
+            float acc = 0.0f;
+            for (int64_t kb = 0; kb < Kg; kb++) {
+                int32_t I = 0;
+                for (int ki = 0; ki < 32; ki++)
+                    I += (int32_t)codes[r * Kg * 32 + kb * 32 + ki] *
+                         (int32_t)blk[kb * 1024 + (ki >> 2) * 128 + noff * 4 + (ki & 3)];
+                acc = fmaf(xs[r * Kg + kb], (float)I, acc);
+            }
+            y[r * ldy + n] = wscales[n] * acc;
+        }
+    }
+    free(codes);
+    free(xs);
+    return 0;
+}
+
+/* embedding_q8c_quant_w (ops/op_embedding.hpp:51-78): per row of the table one scale d = amax / 127 and codes by
+ * quant_row_q8_0 over the whole row (8-wide body half to even, scalar tail half away). */
+int oracle_emb_q8c_quant(const float* w, int64_t V, int64_t E, int8_t* codes, float* scales) {
+    for (int64_t b = 0; b < V; b++) {
+        float s;
+        if (oracle_quant_x(w + b * E, 1, E, (int)E, 1.0f, codes + b * E, &s, NULL)) return 1;
+        scales[b] = s;
+    }
+    return 0;
+}
+
+/* embedding_q8c (ops/op_embedding.hpp:80-137): out[i][k] = scales[id] * (float)codes[id][k]. */
+int oracle_emb_q8c(const int64_t* ids, int64_t n, const int8_t* codes, const float* scales, int64_t E, float* out) {
+    for (int64_t i = 0; i < n; i++)
+        for (int64_t k = 0; k < E; k++) out[i * E + k] = scales[ids[i]] * (float)codes[ids[i] * E + k];
+    return 0;
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

@@ -160,3 +160,39 @@ def test_silu_mul_restatement_against_reference_rows(oracle, golden_dir):
         assert np.allclose(got, ref, rtol=1e-3, atol=1e-4), (i, np.abs(got - ref).max())
         big = np.abs(ref) > 1e-3
         assert (np.abs(got - ref)[big] / np.abs(ref)[big]).max() < 5e-4
+
+
+def test_q8c_restatement_is_bit_equal_to_the_reference(oracle, golden_dir):
+    """FC_quant_Q8C / FC_evaluate_Q8C (ext/llama_ext.cpp:56-113, 232-371) and embedding_q8c_quant_w / embedding_q8c
+    (ops/op_embedding.hpp:51-137) as restated, against what the reference's own compiled code returned."""
+    d = np.load(os.path.join(golden_dir, "q8c_ref.npz"))
+    r = oracle.restated
+    for i in range(int(d["fc_cases"])):
+        wq, ws = r.q8c_pack(d[f"W{i}"])
+        assert np.array_equal(wq, d[f"wq{i}"]) and np.array_equal(ws, d[f"ws{i}"]), i
+        y = r.q8c_fc(d[f"x{i}"], wq, ws, d[f"W{i}"].shape[0])
+        assert np.array_equal(y, d[f"y{i}"]), (i, np.abs(y - d[f"y{i}"]).max())
+    for i in range(int(d["emb_cases"])):
+        codes, scales = r.emb_q8c_quant(d[f"table{i}"])
+        assert np.array_equal(codes, d[f"codes{i}"]) and np.array_equal(scales, d[f"scales{i}"].ravel()), i
+        assert np.array_equal(r.emb_q8c(d[f"ids{i}"], codes, scales), d[f"emb{i}"]), i
+
+
+def test_q8c_edges_of_the_restatement(oracle):
+    r = oracle.restated
+    rng = np.random.default_rng(5)
+    # a zero column has scale 0 and codes 0; N and K need not fill their last block
+    W = rng.standard_normal((40, 70)).astype(np.float32)
+    W[7] = 0
+    wq, ws = r.q8c_pack(W)
+    assert wq.shape == (2, 3, 1024) and ws.shape == (64,)
+    assert ws[7] == 0 and np.all(ws[40:] == 0)
+    x = rng.standard_normal((1, 2, 70)).astype(np.float32)
+    y = r.q8c_fc(x, wq, ws, 40)
+    ref = x.reshape(2, 70) @ W.T
+    assert np.all(y[0, :, 7] == 0) and np.abs(y[0] - ref).max() < 0.05 * np.abs(ref).max()
+    # the table: ties round to even in the 8-wide body and away from zero in the tail
+    t = np.array([[127, 0.5, 1.5, 2.5, -0.5, -1.5, 3, 4, 0.5, 2.5, -2.5]], dtype=np.float32)
+    codes, scales = r.emb_q8c_quant(t)
+    assert scales[0] == 1.0
+    assert codes[0].tolist() == [127, 0, 2, 2, 0, -2, 3, 4, 1, 3, -3]
