@@ -702,7 +702,44 @@ def our_arm(args) -> int:
                                   "weights": sum(cnt * mats_[sh].numel() for sh, cnt in shapes_.items()),
                                   "frac_of_hbm_peak": nbytes / (ms_ * 1e-3) / 1e9 / peak}
             extras["pack_q4_1_llama7b_fc_set_224_matrices"] = full
-            del mats_, Wp
+            del mats_
+            # per-channel int8 weights of the reference's older extension (FC_evaluate_Q8C) and its quantized
+            # embedding table: lm_head-sized FC at M = 1 and 8 (each call = quantizer + FC launch, six packed copies
+            # of the weights in turn so that none stays in L2, replayed as one graph), packer, table look-up
+            q8 = {}
+            Wl = torch.randn((32000, 4096), generator=gen, device=dev, dtype=torch.float32) * 0.02
+            packs_ = [ops.FC_quant_Q8C(Wl) for _ in range(6)]
+            for M_ in (1, 8):
+                xq_ = torch.randn((1, M_, 4096), generator=gen, device=dev, dtype=torch.float32)
+                yq_ = torch.empty((1, M_, 32000), device=dev, dtype=torch.float32)
+                st_ = torch.cuda.Stream(dev)
+                with torch.cuda.stream(st_):
+                    ops.FC_evaluate_Q8C(xq_, packs_[0][0], packs_[0][1], 32000, out=yq_)
+                    st_.synchronize()
+                    g_ = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g_, stream=st_):
+                        for wq_, ws_ in packs_:
+                            ops.FC_evaluate_Q8C(xq_, wq_, ws_, 32000, out=yq_)
+                    ms_ = time_fn(g_.replay, 20) / len(packs_)
+                nb_ = 32000 * 4096 + 32000 * 4 + M_ * 4096 * 4 + M_ * 32000 * 4
+                q8[f"fc_M{M_}_K4096_N32000"] = {"us_per_call": ms_ * 1e3, "gb_s": nb_ / (ms_ * 1e-3) / 1e9,
+                                                "frac_of_hbm_peak": nb_ / (ms_ * 1e-3) / 1e9 / peak,
+                                                "launches_per_call": 2}
+            ms_ = time_fn(lambda: ops.FC_quant_Q8C(Wl), 5)
+            nb_ = Wl.numel() * 5
+            q8["pack_K4096_N32000"] = {"ms": ms_, "gb_s": nb_ / (ms_ * 1e-3) / 1e9, "launches_per_call": 2,
+                                       "frac_of_hbm_peak": nb_ / (ms_ * 1e-3) / 1e9 / peak}
+            ms_ = time_fn(lambda: ops.embedding_q8c_quant_w(Wl), 5)
+            q8["embedding_quant_V32000_E4096"] = {"ms": ms_, "gb_s": nb_ / (ms_ * 1e-3) / 1e9,
+                                                  "frac_of_hbm_peak": nb_ / (ms_ * 1e-3) / 1e9 / peak}
+            codes_, scales_ = ops.embedding_q8c_quant_w(Wl)
+            ids_ = torch.randint(0, 32000, (1, 2048), generator=gen, device=dev)
+            oe_ = torch.empty((1, 2048, 4096), device=dev, dtype=torch.float32)
+            ms_ = time_fn(lambda: ops.embedding_q8c(oe_, ids_, codes_, scales_), 20)
+            q8["embedding_lookup_2048_ids_E4096"] = {"us": ms_ * 1e3, "gb_s": 2048 * 4096 * 5 / (ms_ * 1e-3) / 1e9}
+            ops.check_device_status(dev)
+            extras["q8c"] = q8
+            del Wl, packs_, Wp
         except Exception as e:
             extras = {"error": str(e)}
 

@@ -92,13 +92,22 @@ def _op_class(module: str, name: str) -> type:
     return _op_classes[key]
 
 
+# Everything else a saved model refers to: numpy's array reconstruction.  No other global is resolved, so that a
+# file from an unknown source cannot name a callable of its choosing (the reference's own pickle.load can).
+_NUMPY_GLOBALS = {(m, n) for m in ("numpy", "numpy.core.multiarray", "numpy._core.multiarray", "numpy.core.numeric",
+                                   "numpy._core.numeric")
+                  for n in ("_reconstruct", "ndarray", "dtype", "scalar", "_frombuffer")}
+
+
 class _Unpickler(pickle.Unpickler):
     def find_class(self, module: str, name: str):
         if module == _TENSOR_MODULE and name == _TENSOR_NAME:
             return HostTensor
         if module in _OP_MODULES and name.startswith("llmop_"):
             return _op_class(module, name)
-        return super().find_class(module, name)
+        if (module, name) in _NUMPY_GLOBALS:
+            return super().find_class(module, name)
+        raise pickle.UnpicklingError(f"a saved model does not refer to {module}.{name}: refusing to resolve it")
 
 
 def load(path_or_file):
@@ -204,6 +213,28 @@ def fc_ops(model, device="cuda") -> dict:
         if isinstance(bias, HostTensor) and bias.numel() > 0:
             gpu.bias = torch.from_numpy(np.ascontiguousarray(bias.numpy(), dtype=np.float32)).to(device)
         gpu.N = int(op.N)
+        out[path] = gpu
+    return out
+
+
+def embedding_ops(model, device="cuda") -> dict:
+    """``{path: ops.llmop_embedding_q8c}`` for every ``llmop_embedding_q8c`` of a loaded model: its int8 codes and
+    fp32 scales copied to ``device`` as they are."""
+    import torch
+
+    from .ops import llmop_embedding_q8c
+
+    out = {}
+    for path, op in walk_ops(model):
+        if type(op).__name__ != "llmop_embedding_q8c":
+            continue
+        codes, scales = op.weight.numpy(), op.scales.numpy()
+        if codes.dtype != np.int8 or codes.ndim != 2 or scales.dtype != np.float32 or scales.shape != codes.shape[:1]:
+            raise RuntimeError(f"{path}: expected int8 [V, E] codes and fp32 [V] scales, got "
+                               f"{codes.dtype}{list(codes.shape)} / {scales.dtype}{list(scales.shape)}")
+        gpu = llmop_embedding_q8c.__new__(llmop_embedding_q8c)
+        gpu.weight = torch.from_numpy(np.ascontiguousarray(codes)).to(device)
+        gpu.scales = torch.from_numpy(np.ascontiguousarray(scales)).to(device)
         out[path] = gpu
     return out
 

@@ -41,6 +41,7 @@
 // CTA to arrive adds the slots in CTA order.  There is no spin-wait anywhere
 // and the result does not depend on timing.
 #include "common.cuh"
+#include "decode_math.cuh"
 
 namespace q4fc {
 namespace {
@@ -62,14 +63,6 @@ struct DecodeParams {
     int code_stride;  // bytes between code rows in shared memory
     int x_vec_ok, y_vec_ok;
 };
-
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // CTA that owns block b under the split start(c) = floor(c*T/P)
 __device__ __forceinline__ int cta_of_block(int64_t b, int64_t T, int64_t P) { return (int)(((b + 1) * P + T - 1) / T - 1); }
@@ -144,63 +137,28 @@ __global__ void __launch_bounds__(kDecThreads, 2) fc_decode_kernel(const DecodeP
             const int row = u / chunks, c = u % chunks;
             const int64_t k = (int64_t)c * 128 + lane * 4;
             const float* src = p.x + row * p.ldx + k;
-            float v[4];
+            float v[1][4];
             if (p.x_vec_ok && k + 4 <= p.K) {
                 float4 a = __ldcg(reinterpret_cast<const float4*>(src));
-                v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+                v[0][0] = a.x, v[0][1] = a.y, v[0][2] = a.z, v[0][3] = a.w;
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; j++) v[j] = (k + j < p.K) ? __ldcg(src + j) : 0.0f;
+                for (int j = 0; j < 4; j++) v[0][j] = (k + j < p.K) ? __ldcg(src + j) : 0.0f;
             }
             const int kb = c * GPC + lane / SEG;
             const bool exists = kb < p.Kg;
             const int len = exists ? (int)min((int64_t)G, p.K - (int64_t)kb * G) : 0;
-            const int body = (len / 8) * 8;
-            const int e0 = (lane % SEG) * 4;
-            float amax = 0.0f, fsum = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 4; j++)
-                if (e0 + j < len) {
-                    amax = fmaxf(amax, fabsf(v[j]));
-                    fsum += v[j];
-                }
-#pragma unroll
-            for (int off = SEG / 2; off > 0; off >>= 1) {
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off, SEG));
-                fsum += __shfl_xor_sync(0xffffffffu, fsum, off, SEG);
-            }
-            const float d = div_const_rn(amax, 127.0f, 1.0f / 127.0f);
-            const float id = inv_or_zero(d);
-            uint32_t packed = 0;
-            int isum = 0;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int e = e0 + j;
-                int q = 0;
-                if (e < len) {
-                    const float tq = __fmul_rn(v[j], id);
-                    if (e < body) {
-                        q = __float2int_rn(tq);
-                    } else {
-                        const float h = __int_as_float((__float_as_int(tq) & 0x80000000) | 0x3F000000);
-                        q = __float2int_rz(__fadd_rz(tq, h));
-                    }
-                    q = min(127, max(-128, q));
-                }
-                isum += q;
-                packed |= (uint32_t)(q & 0xFF) << (8 * j);
-            }
-            if (SIGNED) {
-#pragma unroll
-                for (int off = SEG / 2; off > 0; off >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, off, SEG);
-            }
+            uint32_t pk[1];
+            float dq[1], aux[1];
+            q8_quantize_rows<G, 1, SIGNED>(v, lane, len, pk, dq, aux);  // the arithmetic every decode kernel shares
+            const uint32_t packed = pk[0];
             if (exists) {
                 *reinterpret_cast<uint32_t*>(codes + (int64_t)row * p.code_stride + k) = packed;
                 if (lane % SEG == 0) {
                     // reference: x_scales = d * scale with scale = 1/16 for Q4_0, cancelled by its
                     // x16 nibble shift; both are exact powers of two and are left out here
-                    sc[kb * 16 + row * 2 + 0] = d;
-                    sc[kb * 16 + row * 2 + 1] = SIGNED ? __int_as_float(8 * isum) : fsum;
+                    sc[kb * 16 + row * 2 + 0] = dq[0];
+                    sc[kb * 16 + row * 2 + 1] = aux[0];
                 }
             }
         }

@@ -1,6 +1,5 @@
 // Single-GPU instantiations of the decode kernel (fc_decode_ring_impl.cuh, TP = false), and the status
 // word its kernels use when the caller passes no workspace.
-#define Q4FC_TL_NAME q4fc_dbg_set_tl
 #include "fc_decode_ring_impl.cuh"
 
 namespace q4fc {

@@ -1,7 +1,6 @@
 // Multi-GPU instantiations of the decode kernel (fc_decode_ring_impl.cuh, TP = true): outputs leave as
 // epoch-stamped 64-bit words stored into every rank's buffer, inputs may be such a buffer.  Also the two
 // small kernels around them: the step barrier and the unpacking of a stamped buffer.
-#define Q4FC_TL_NAME q4fc_dbg_set_tl_tp
 #include "fc_decode_ring_impl.cuh"
 
 namespace q4fc {

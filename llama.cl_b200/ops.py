@@ -1,5 +1,7 @@
 """``llmop_fc_q4a``: the callable the reference's model builds for every
-``nn.Linear`` (``chatllama/main.py:158-177``), on the GPU kernels."""
+``nn.Linear`` (``chatllama/main.py:158-177``), and ``llmop_embedding_q8c``, the
+one it builds for the token table (``chatllama/main.py:207-219``), on the GPU
+kernels."""
 from __future__ import annotations
 
 import torch
@@ -39,3 +41,22 @@ class llmop_fc_q4a:
 
     def __repr__(self) -> str:
         return f"llmop_fc_q4a(weight: {list(self.weight.shape)})"
+
+
+class llmop_embedding_q8c:
+    """Quantizes the table at construction (one scale per row), ``__call__(input_ids)`` looks rows up and
+    dequantizes them.  Attributes as in the reference: ``weight`` (int8 codes ``[V, E]``), ``scales`` (``[V]``)."""
+
+    def __init__(self, weight: torch.Tensor, *, device=None) -> None:
+        w = weight.detach()
+        dev = torch.device(device) if device is not None else (w.device if w.is_cuda else torch.device("cuda"))
+        self.weight, self.scales = llmops.embedding_q8c_quant_w(w.to(device=dev, dtype=torch.float32).contiguous())
+
+    def __call__(self, input_ids: torch.Tensor) -> torch.Tensor:
+        ids = input_ids.to(self.weight.device).contiguous()
+        output = torch.empty(tuple(ids.shape) + (self.weight.shape[1],), dtype=torch.float32, device=self.weight.device)
+        llmops.embedding_q8c(output, ids, self.weight, self.scales)
+        return output
+
+    def __repr__(self) -> str:
+        return f"llmop_embedding_q8c(weight: {list(self.weight.shape)})"

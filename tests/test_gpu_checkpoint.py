@@ -35,3 +35,21 @@ def test_reference_checkpoint_runs_on_the_gpu(lib_built):
     target = dict(checkpoint.walk_ops(model))[first]
     checkpoint.store_fc(target, ops[first])
     assert checkpoint.dumps(model) == open(PKL, "rb").read()
+
+
+def test_reference_checkpoint_embedding_table_on_the_gpu(lib_built):
+    """The quantized token table of a saved model (llmop_embedding_q8c: int8 codes, one scale per row) goes to the
+    device as it is; a look-up returns scale * code, the reference's arithmetic, bit for bit."""
+    from llama_cl_b200 import checkpoint
+
+    model = checkpoint.load(PKL)
+    embs = checkpoint.embedding_ops(model, "cuda")
+    assert list(embs) == ["op_dict.model.embed_tokens"]
+    op = embs["op_dict.model.embed_tokens"]
+    host = dict(checkpoint.walk_ops(model))["op_dict.model.embed_tokens"]
+    codes, scales = host.weight.numpy(), host.scales.numpy()
+    V = codes.shape[0]
+    ids = np.array([[0, V - 1, 3 % V, 1 % V]], dtype=np.int64)
+    got = op(torch.from_numpy(ids)).cpu().numpy()
+    want = scales[ids][..., None] * codes[ids].astype(np.float32)
+    assert got.shape == (1, 4, codes.shape[1]) and np.array_equal(got, want)
