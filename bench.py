@@ -427,7 +427,7 @@ def our_arm(args) -> int:
     run_step = capture(step_device)
     # the timed region: args.steps steps, each replayed `inner` times so that the region lasts about half a second
     probe_ms, _ = timed(run_step, 20, warm=warmup)
-    inner = max(1, int(round(TIMED_REGION_S * 1e3 / max(probe_ms * args.steps, 1e-6))))
+    inner = max(1, int(round(args.region_s * 1e3 / max(probe_ms * args.steps, 1e-6))))
     if distributed:
         t = torch.tensor([inner], device=dev, dtype=torch.int64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)  # the same count on every rank: the step holds a cross-rank barrier
@@ -445,7 +445,7 @@ def our_arm(args) -> int:
     # ---- the dominant kernel alone: the FC launches of a step with their inputs already quantized
     if not distributed:
         run_fc = capture(step_fc_only)
-        n_fc = max(20, min(2000, int(0.2e3 / max(probe_ms, 1e-3))))
+        n_fc = max(20, min(2000, int(0.4 * args.region_s * 1e3 / max(probe_ms, 1e-3))))
         ms_fc, _ = timed(run_fc, n_fc)
     else:
         ms_fc = ms_step
@@ -544,8 +544,8 @@ def our_arm(args) -> int:
                      "what": "Q4_1 group-128 FC stack of a random-init 32-layer Llama-7B (hidden 4096, intermediate "
                              "11008, vocab 32000 lm_head), batch 1"}
             if not distributed:
-                for glue in ("none", "llama"):
-                    st = DecodeFCStack(layers, lm_head, hidden=H, intermediate=I, vocab=V, rows=1, glue=glue)
+                for glue, chain in (("none", False), ("llama", False), ("none", True), ("llama", True)):
+                    st = DecodeFCStack(layers, lm_head, hidden=H, intermediate=I, vocab=V, rows=1, glue=glue, chain=chain)
                     st.forward(h0, sync=True)
                     n_tok = max(3, min(args.steps * inner, 100))
                     with torch.cuda.stream(st.stream):
@@ -558,6 +558,14 @@ def our_arm(args) -> int:
                         a1.record()
                     st.stream.synchronize()
                     ms_tok = a0.elapsed_time(a1) / n_tok
+                    if chain:
+                        # the same schedule as ONE persistent launch (q4fc_fc_chain_*): reported beside the graph of
+                        # launches, whichever is faster
+                        st.check()
+                        stack.setdefault("one_persistent_launch", {})[
+                            "ms_per_token" if glue == "none" else "ms_per_token_with_norms_and_mlp_glue"] = ms_tok
+                        del st
+                        continue
                     key = "ms_per_token" if glue == "none" else "ms_per_token_with_norms_and_mlp_glue"
                     stack[key] = ms_tok
                     stack["launches_per_token" if glue == "none" else "launches_per_token_with_glue"] = \
@@ -864,6 +872,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tp", default="fused", choices=["fused", "nccl"],
                     help="with --gpus N > 1: how the ranks' output columns meet")
+    ap.add_argument("--region-s", type=float, default=TIMED_REGION_S,
+                    help="length of the timed region in seconds: every step is replayed as often as it takes "
+                         "(a profiler run asks for 0: every step once)")
     ap.add_argument("--sections", default="e2e,stack,extras,cpu,percall,nccl",
                     help="optional legs beside the timed sweep (a profiler run asks for none of them: --sections none)")
     args = ap.parse_args()

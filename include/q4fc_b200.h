@@ -319,6 +319,46 @@ int q4fc_tp_collect_multi(const unsigned long long* const* stamped, const int64_
                           const int64_t* ld, float* const* dst, const int64_t* ldd, int n,
                           const unsigned long long* epoch, int* status, q4fc_stream_t stream);
 
+/* ---- a chain of dependent decode FCs in one launch -------------------------------------------------------------
+ *
+ * Replaces a run of the reference's Model.forward (chatllama/main.py:331-380): per layer the fc_Q4A calls q, k, v |
+ * o | gate, up | down, each fed by the one before through llmops.rmsnorm (ops/op_misc.hpp:142-181), llmops.iadd
+ * (:55-79), llmops.itrans("silu") and llmops.imul (:83-138), and lm_head at the end.  One persistent kernel runs all
+ * steps: the weight stream never stops at a step boundary, only the activations wait (a grid barrier per step).
+ *
+ * A step: one input x (fp32 [rows][ldx], rows <= 8, K % 8 == 0, 16-byte aligned, ldx % 4 == 0; written by an earlier
+ * step of the chain or by work ordered before the launch), a transform applied to it before it is quantized
+ *   Q4FC_CHAIN_PLAIN     none
+ *   Q4FC_CHAIN_RMSNORM   (x / sqrt(mean(x^2) + eps)) * aux[k]          aux: fp32 [K]
+ *   Q4FC_CHAIN_SILU_MUL  aux[m][k] * silu(x[m][k])                     aux: fp32 [rows][ldx] (the up projection)
+ * and njobs >= 1 jobs (q4fc_fc_job: weights, output, optional addend = bias or residual) that multiply it; the jobs
+ * of all steps follow one another in `jobs`.  A job must not write the input of its own step; a buffer may be
+ * reused by later steps.  Per step the values are those of q4fc_rmsnorm_quant / q4fc_silu_mul_quant /
+ * q4fc_quant_x_q8 followed by q4fc_fc_decode_multi (same codes bit for bit; outputs within rounding of the fp32 sums).
+ *
+ *   q4fc_fc_chain_create   checks the steps, uploads their tables (cudaMalloc + synchronous copies: not inside a
+ *                          stream capture) and returns a handle bound to the current device.
+ *   q4fc_fc_chain_run      one cooperative launch of one CTA per SM on `stream`; asynchronous; may be captured into
+ *                          a CUDA graph.  Launches of one handle must not overlap on the GPU.
+ *   q4fc_fc_chain_check    host-synchronous: Q4FC_OK, or Q4FC_EDEVICE when a bounded wait inside a launch ran out
+ *                          (results invalid; the handle is usable again).
+ *   q4fc_fc_chain_destroy  frees the handle (after its launches have completed). */
+enum { Q4FC_CHAIN_PLAIN = 0, Q4FC_CHAIN_RMSNORM = 1, Q4FC_CHAIN_SILU_MUL = 2 };
+typedef struct q4fc_chain_step {
+    const float* x;
+    int64_t ldx;
+    int64_t K;
+    int transform;
+    float eps;        /* RMSNORM */
+    const float* aux; /* RMSNORM: weight; SILU_MUL: up */
+    int njobs;
+} q4fc_chain_step;
+int q4fc_fc_chain_create(const q4fc_chain_step* steps, int nsteps, const q4fc_fc_job* jobs, int njobs, int64_t rows,
+                         int qtype, int group_k, void** chain);
+int q4fc_fc_chain_run(void* chain, q4fc_stream_t stream);
+int q4fc_fc_chain_check(void* chain, q4fc_stream_t stream);
+int q4fc_fc_chain_destroy(void* chain);
+
 /* ---- per-channel int8 weights ("Q8C"): the FC of the reference's older extension and its embedding table ------
  *
  *   q4fc_q8c_pack         replaces FC_quant_Q8C (ext/llama_ext.cpp:56-113).  w: fp32 row-major [N][K] on the device.

@@ -28,6 +28,7 @@ SYMBOLS = (
     "q4fc_fc_decode_tp_batch", "q4fc_tp_collect_multi",
     "q4fc_xq_bytes", "q4fc_quant_x_q8", "q4fc_rmsnorm_quant", "q4fc_add_rmsnorm_quant", "q4fc_fc_decode_q8",
     "q4fc_silu_mul_quant",
+    "q4fc_fc_chain_create", "q4fc_fc_chain_run", "q4fc_fc_chain_check", "q4fc_fc_chain_destroy",
     "q4fc_q8c_pack", "q4fc_q8c_workspace_bytes", "q4fc_q8c_fc", "q4fc_emb_q8c_quant", "q4fc_emb_q8c",
 )
 
@@ -57,6 +58,22 @@ class FcJob(C.Structure):
         ("addend", C.c_void_p),
         ("ld_addend", C.c_int64),
     ]
+
+
+class ChainStep(C.Structure):
+    """``q4fc_chain_step`` of include/q4fc_b200.h."""
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("ldx", C.c_int64),
+        ("K", C.c_int64),
+        ("transform", C.c_int),
+        ("eps", C.c_float),
+        ("aux", C.c_void_p),
+        ("njobs", C.c_int),
+    ]
+
+
+CHAIN_PLAIN, CHAIN_RMSNORM, CHAIN_SILU_MUL = 0, 1, 2
 
 
 class TpCall(C.Structure):
@@ -132,6 +149,10 @@ def lib() -> C.CDLL:
     L.q4fc_add_rmsnorm_quant.argtypes = [vp, vp, vp, i64, i64, i64, vp, f32, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_silu_mul_quant.argtypes = [vp, vp, i64, i64, i64, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_fc_decode_q8.argtypes = [vp, i64, i64, vp, i64, i64, i32, i32, i64, vp, i64, u32, vp]
+    L.q4fc_fc_chain_create.argtypes = [C.POINTER(ChainStep), i32, C.POINTER(FcJob), i32, i64, i32, i32, C.POINTER(vp)]
+    L.q4fc_fc_chain_run.argtypes = [vp, vp]
+    L.q4fc_fc_chain_check.argtypes = [vp, vp]
+    L.q4fc_fc_chain_destroy.argtypes = [vp]
     L.q4fc_q8c_pack.argtypes = [vp, i64, i64, vp, vp, vp]
     L.q4fc_q8c_workspace_bytes.restype = sz
     L.q4fc_q8c_workspace_bytes.argtypes = [i64, i64]

@@ -640,6 +640,42 @@ int q4fc_tp_collect_multi(const unsigned long long* const* stamped, const int64_
     return launch_tp_collect_multi(stamped, rows, N, ld, dst, ldd, n, epoch, status, static_cast<cudaStream_t>(stream));
 }
 
+int q4fc_fc_chain_create(const q4fc_chain_step* steps, int nsteps, const q4fc_fc_job* jobs, int njobs, int64_t rows,
+                         int qtype, int group_k, void** chain) {
+    if (!valid_variant(qtype, group_k)) {
+        set_error("fc_chain: qtype=%d, group_k=%d is not a block type", qtype, group_k);
+        return Q4FC_EVARIANT;
+    }
+    if (!steps || !jobs || !chain || nsteps <= 0 || njobs <= 0) {
+        set_error("fc_chain: null pointer or no steps");
+        return Q4FC_EINVAL;
+    }
+    if (rows < 1 || rows > kMaxDecodeRows) {
+        set_error("fc_chain: rows=%lld outside 1..%d", (long long)rows, kMaxDecodeRows);
+        return Q4FC_ELIMIT;
+    }
+    *chain = nullptr;
+    return chain_create(steps, nsteps, jobs, njobs, (int)rows, qtype, group_k, chain);
+}
+
+int q4fc_fc_chain_run(void* chain, q4fc_stream_t stream) {
+    if (!chain) {
+        set_error("fc_chain: null handle");
+        return Q4FC_EINVAL;
+    }
+    return chain_run(chain, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_fc_chain_check(void* chain, q4fc_stream_t stream) {
+    if (!chain) {
+        set_error("fc_chain: null handle");
+        return Q4FC_EINVAL;
+    }
+    return chain_check(chain, static_cast<cudaStream_t>(stream));
+}
+
+int q4fc_fc_chain_destroy(void* chain) { return chain_destroy(chain); }
+
 int q4fc_q8c_pack(const float* w, int64_t N, int64_t K, int8_t* wq, float* wscales, q4fc_stream_t stream) {
     if (N < 0 || K < 0) {
         set_error("q8c_pack: negative size");

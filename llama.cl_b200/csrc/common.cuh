@@ -105,6 +105,12 @@ int launch_q8c_fc(const float* x, int64_t rows, int64_t K, int64_t ldx, const in
 int launch_emb_q8c_quant(const float* table, int64_t V, int64_t E, int8_t* codes, float* scales, cudaStream_t s);
 int launch_emb_q8c(const void* ids, int ids_are_i32, int64_t n, const int8_t* codes, const float* scales, int64_t V,
                    int64_t E, float* out, int64_t ldo, cudaStream_t s);
+// a chain of dependent decode FCs as one persistent launch (fc_chain.cu)
+int chain_create(const q4fc_chain_step* steps, int nsteps, const q4fc_fc_job* jobs, int njobs, int rows, int qtype, int G,
+                 void** out);
+int chain_run(void* chain, cudaStream_t s);
+int chain_check(void* chain, cudaStream_t s);
+int chain_destroy(void* chain);
 size_t prefill_workspace_bytes(int64_t rows, int64_t K, int64_t N, int qtype, int G);
 int launch_fc_prefill(const float* x, int64_t rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                       int64_t Kg, int qtype, int G, int64_t N, float* y, int64_t ldy, void* ws, size_t ws_bytes,

@@ -25,19 +25,19 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
 // from zero).  Out per row: the 4 codes packed little-endian, the scale d = amax/127 (IEEE division), and
 // `aux` = the tree-ordered sum of the group's raw values, or with SIGNED the bits of 8 * (sum of codes).
 // The reference's 1/16 activation scale of Q4_0 and its x16 nibble shift cancel exactly; neither is applied.
+// The rows may have different `len` (q8_quantize_rows_v: rows that are different 128-k chunks of one activation row).
 template <int G, int ROWS, bool SIGNED>
-__device__ __forceinline__ void q8_quantize_rows(const float (&v)[ROWS][4], int lane, int len, uint32_t (&packed)[ROWS],
-                                                 float (&d)[ROWS], float (&aux)[ROWS]) {
+__device__ __forceinline__ void q8_quantize_rows_v(const float (&v)[ROWS][4], int lane, const int (&lens)[ROWS],
+                                                   uint32_t (&packed)[ROWS], float (&d)[ROWS], float (&aux)[ROWS]) {
     constexpr int SEG = G / 4;
     const int e0 = (lane % SEG) * 4;
-    const int body = len & ~7;
     float amax[ROWS], fsum[ROWS];
 #pragma unroll
     for (int m = 0; m < ROWS; m++) {
         amax[m] = 0.0f, fsum[m] = 0.0f;
 #pragma unroll
         for (int j = 0; j < 4; j++)
-            if (e0 + j < len) {
+            if (e0 + j < lens[m]) {
                 amax[m] = fmaxf(amax[m], fabsf(v[m][j]));
                 fsum[m] += v[m][j];
             }
@@ -60,9 +60,9 @@ __device__ __forceinline__ void q8_quantize_rows(const float (&v)[ROWS][4], int 
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             int q = 0;
-            if (e0 + j < len) {
+            if (e0 + j < lens[m]) {
                 const float tq = __fmul_rn(v[m][j], id);
-                if (e0 + j < body) {
+                if (e0 + j < (lens[m] & ~7)) {
                     q = __float2int_rn(tq);  // nearest even
                 } else {
                     const float h = __int_as_float((__float_as_int(tq) & 0x80000000) | 0x3F000000);
@@ -82,6 +82,15 @@ __device__ __forceinline__ void q8_quantize_rows(const float (&v)[ROWS][4], int 
     }
 }
 
+template <int G, int ROWS, bool SIGNED>
+__device__ __forceinline__ void q8_quantize_rows(const float (&v)[ROWS][4], int lane, int len, uint32_t (&packed)[ROWS],
+                                                 float (&d)[ROWS], float (&aux)[ROWS]) {
+    int lens[ROWS];
+#pragma unroll
+    for (int m = 0; m < ROWS; m++) lens[m] = len;
+    q8_quantize_rows_v<G, ROWS, SIGNED>(v, lane, lens, packed, d, aux);
+}
+
 // One block (32 columns x G k) against <= 8 activation rows, for lane (g = lane >> 2, t = lane & 3):
 //   q[j]   the lane's 128 bits of set j (block rows 4j + t, columns 4g..4g+3: byte offset (4j+t)*128 + 16g)
 //   wd/wm  fp16 scales / minima of columns 4g..4g+3
@@ -96,7 +105,9 @@ __device__ __forceinline__ void q8_quantize_rows(const float (&v)[ROWS][4], int 
 // IH is a multiple of 16 and everything stays below 2^24.  The integer ALU is the scarce pipe of this kernel;
 // the conversions (XU pipe) and the extra FMA are free by comparison.
 // Group 32 (one set): low nibbles in the first half of the MMA's k, shifted high nibbles in the second.
-template <int G, int QTYPE, bool SIGNED>
+// MI = 1 (a launch with one activation row): only row 2t of the lane's two rows is converted and scaled; acc[c][1]
+// is left as it is.
+template <int G, int QTYPE, bool SIGNED, int MI = 2>
 __device__ __forceinline__ void block_accumulate(const uint4 (&q)[G / 32], uint2 wd, uint2 wm, const uint8_t* codes,
                                                  bool row_live, const float* sc, int t, float (&acc)[4][2]) {
     constexpr int SETS = G / 32;
@@ -135,7 +146,7 @@ __device__ __forceinline__ void block_accumulate(const uint4 (&q)[G / 32], uint2
 #pragma unroll
         for (int c = 0; c < 4; c++) {
 #pragma unroll
-            for (int mi = 0; mi < 2; mi++) {
+            for (int mi = 0; mi < MI; mi++) {
                 int L = il[c][mi];
                 if (SIGNED) L -= __float_as_int(gs[mi]);
                 // |IL|, |IH|/16 <= 15 * 127 * 64 and their sum < 2^24: every step is exact
@@ -162,7 +173,7 @@ __device__ __forceinline__ void block_accumulate(const uint4 (&q)[G / 32], uint2
 #pragma unroll
         for (int c = 0; c < 4; c++) {
 #pragma unroll
-            for (int mi = 0; mi < 2; mi++) {
+            for (int mi = 0; mi < MI; mi++) {
                 int I = iv[c][mi];
                 if (SIGNED) I -= __float_as_int(gs[mi]);
                 fI[c][mi] = __int2float_rn(I);  // |I| <= 15 * 127 * 32: exact
@@ -181,7 +192,7 @@ __device__ __forceinline__ void block_accumulate(const uint4 (&q)[G / 32], uint2
 #pragma unroll
     for (int c = 0; c < 4; c++) {
 #pragma unroll
-        for (int mi = 0; mi < 2; mi++) {
+        for (int mi = 0; mi < MI; mi++) {
             acc[c][mi] = fmaf(__fmul_rn(wdf[c], xs[mi]), fI[c][mi], acc[c][mi]);
             if (QTYPE == 1) acc[c][mi] = fmaf(wmf[c], gs[mi], acc[c][mi]);
         }

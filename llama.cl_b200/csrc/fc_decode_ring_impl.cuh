@@ -43,6 +43,7 @@
 
 #include "common.cuh"
 #include "decode_math.cuh"
+#include "ring_ptx.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -59,7 +60,6 @@ constexpr int kMaxTpJobs = 4;   // weight tensors per launch in the multi-GPU fo
 constexpr int kMaxUnits = 160;  // work units (CTAs, or clusters) per launch: bounds the table of first stripes
 constexpr int kShare = 4;       // CTAs that share the quantization of the activations (cs == 1)
 constexpr int kMaxOwned = 16;   // stripes per cluster when cs > 1 (bounds the inbox)
-constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 
 struct RingJobDev {
     const uint8_t* wq;
@@ -101,60 +101,8 @@ struct RingParams {
     const unsigned long long* epoch;
 };
 
-// ---- PTX wrappers -------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// 1-D bulk copy global -> this CTA's shared memory; bytes % 16 == 0, both addresses 16-byte aligned
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
-// Bounded wait on an mbarrier phase.  Once one wait of the CTA has run out (*fail != 0) all others end at once.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* fail, int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return;
-    const unsigned long long t0 = globaltimer_ns();
-    for (unsigned it = 1;; it++) {
-        if (mbar_try_wait(bar, parity)) return;
-        if ((it & 255) == 0) {
-            if (*fail != 0) return;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
-                *fail = 1;
-                atomicCAS(status, 0, code);
-                return;
-            }
-        }
-    }
-}
 
 __device__ __forceinline__ unsigned long long ld_stamped(const unsigned long long* a) {
     unsigned long long w;

@@ -24,7 +24,7 @@ from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, FLAG_STREAMK, Q4_0, Q4_1
 
 __all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
            "fc_workspace", "Workspace", "fc_Q4A_multi", "FCBatch", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize", "silu_mul_quantize",
-           "QuantizedActivations", "FC_quant_Q8C", "FC_evaluate_Q8C", "embedding_q8c_quant_w", "embedding_q8c", "check_device_status"]
+           "QuantizedActivations", "FCChain", "FC_quant_Q8C", "FC_evaluate_Q8C", "embedding_q8c_quant_w", "embedding_q8c", "check_device_status"]
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -465,6 +465,123 @@ class FCBatch:
             _cabi.check(_cabi.lib().q4fc_fc_decode_batch(self._args, self.n, self.qtype, self.group_k, self.flags,
                                                          _stream_ptr(self.device)), "fc_decode_batch")
         return self.outs
+
+
+class FCChain:
+    """A chain of dependent decode FCs that runs as ONE persistent launch (``q4fc_fc_chain_*``): the weight stream
+    does not stop between the steps, only the activations wait for the step before.
+
+    ``steps``: a list of dicts, in execution order:
+        ``x``          fp32 CUDA tensor ``[1, rows, K]`` (or ``[rows, K]``): the step's input -- an output of an earlier
+                       step, or a tensor the caller fills before ``run()``;
+        ``transform``  ``"plain"`` (default), ``"rmsnorm"`` (``aux`` = weight ``[K]``, ``eps``) or ``"silu_mul"``
+                       (``aux`` = the up projection, same shape as ``x``: the value quantized is ``aux * silu(x)``);
+        ``jobs``       ``[(wei_quantized, N, out), ...]`` or ``(wei_quantized, N, out, addend)``: weight tensors that
+                       multiply the step's input, ``out`` fp32 ``[1, rows, N]``, ``addend`` a bias ``[N]`` or a tensor of
+                       ``out``'s shape (the residual stream) added to the result.
+    All weights share one block type; ``rows <= 8``; ``K % 8 == 0``.  The tables are uploaded once; ``run()`` only
+    launches (asynchronous on the current stream, capturable in a CUDA graph); ``check()`` waits and raises if a
+    bounded wait inside the kernel ran out."""
+
+    _TRANSFORMS = {"plain": _cabi.CHAIN_PLAIN, "rmsnorm": _cabi.CHAIN_RMSNORM, "silu_mul": _cabi.CHAIN_SILU_MUL}
+
+    def __init__(self, steps) -> None:
+        if not steps:
+            raise RuntimeError("FCChain: no steps")
+        njobs = sum(len(s["jobs"]) for s in steps)
+        self._steps = (_cabi.ChainStep * len(steps))()
+        self._jobs = (_cabi.FcJob * max(njobs, 1))()
+        self._keep = []
+        self._handle = None
+        q = G = rows = None
+        jn = 0
+        for i, s in enumerate(steps):
+            x = s["x"]
+            if not isinstance(x, torch.Tensor) or x.dtype != torch.float32 or not x.is_cuda or not x.is_contiguous():
+                raise RuntimeError(f"steps[{i}].x: expected a contiguous fp32 CUDA tensor")
+            K = int(x.shape[-1])
+            r = x.numel() // K
+            if rows is None:
+                rows, self.device = r, x.device
+            elif r != rows:
+                raise RuntimeError(f"steps[{i}].x has {r} rows, the chain {rows}")
+            tname = s.get("transform", "plain")
+            if tname not in self._TRANSFORMS:
+                raise RuntimeError(f"steps[{i}].transform={tname!r}: expected one of {sorted(self._TRANSFORMS)}")
+            aux = s.get("aux")
+            if tname == "rmsnorm":
+                _require_cuda(aux, f"steps[{i}].aux", torch.float32, 1)
+                if aux.numel() != K:
+                    raise RuntimeError(f"steps[{i}].aux: rmsnorm weight of {aux.numel()} values for K={K}")
+            elif tname == "silu_mul":
+                if not isinstance(aux, torch.Tensor) or aux.dtype != torch.float32 or tuple(aux.shape) != tuple(x.shape) \
+                        or not aux.is_cuda or not aux.is_contiguous():
+                    raise RuntimeError(f"steps[{i}].aux: silu_mul needs the up projection, a tensor like x")
+            elif aux is not None:
+                raise RuntimeError(f"steps[{i}]: a plain step takes no aux")
+            if not s["jobs"]:
+                raise RuntimeError(f"steps[{i}]: no jobs")
+            st = self._steps[i]
+            st.x, st.ldx, st.K = x.data_ptr(), K, K
+            st.transform, st.eps = self._TRANSFORMS[tname], float(s.get("eps", 0.0))
+            st.aux, st.njobs = (aux.data_ptr() if aux is not None else None), len(s["jobs"])
+            self._keep.append((x, aux))
+            for job in s["jobs"]:
+                w, N, out = job[0], int(job[1]), job[2]
+                addend = job[3] if len(job) > 3 else None
+                _require_cuda(w, f"steps[{i}] weights", torch.int8, 3)
+                qi, Gi = _cabi.infer_variant(w.shape[2])
+                if q is None:
+                    q, G = qi, Gi
+                elif (qi, Gi) != (q, G):
+                    raise RuntimeError("FCChain: the weight tensors differ in block type")
+                if int(w.shape[1]) != (K + Gi - 1) // Gi:
+                    raise RuntimeError(f"steps[{i}]: weights hold {w.shape[1]} K groups, the input needs {(K + Gi - 1) // Gi}")
+                if not isinstance(out, torch.Tensor) or out.dtype != torch.float32 or not out.is_cuda \
+                        or not out.is_contiguous() or out.numel() != rows * N or int(out.shape[-1]) != N:
+                    raise RuntimeError(f"steps[{i}] out: expected a contiguous fp32 CUDA tensor [..., {rows}, {N}]")
+                a = self._jobs[jn]
+                a.wq, a.Ng, a.N, a.y, a.ldy = w.data_ptr(), int(w.shape[0]), N, out.data_ptr(), N
+                a.addend, a.ld_addend = None, 0
+                if addend is not None:
+                    if not isinstance(addend, torch.Tensor) or addend.dtype != torch.float32 or not addend.is_cuda \
+                            or not addend.is_contiguous():
+                        raise RuntimeError(f"steps[{i}] addend: expected a contiguous fp32 CUDA tensor")
+                    if addend.numel() == N:
+                        a.addend, a.ld_addend = addend.data_ptr(), 0  # one row for all: a bias
+                    elif addend.numel() == rows * N and int(addend.shape[-1]) == N:
+                        a.addend, a.ld_addend = addend.data_ptr(), N
+                    else:
+                        raise RuntimeError(f"steps[{i}] addend: expected [{N}] or the shape of out")
+                self._keep.append((w, out, addend))
+                jn += 1
+        self.rows, self.qtype, self.group_k, self.nsteps, self.njobs = rows, q, G, len(steps), njobs
+        h = _cabi.C.c_void_p()
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.lib().q4fc_fc_chain_create(self._steps, len(steps), self._jobs, njobs, rows, q, G,
+                                                         _cabi.C.byref(h)), "FCChain")
+        self._handle = h
+
+    def run(self) -> None:
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.lib().q4fc_fc_chain_run(self._handle, _stream_ptr(self.device)), "FCChain.run")
+
+    def check(self) -> None:
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.lib().q4fc_fc_chain_check(self._handle, _stream_ptr(self.device)), "FCChain.check")
+
+    def close(self) -> None:
+        if self._handle is not None:
+            h, self._handle = self._handle, None
+            with torch.cuda.device(self.device):
+                torch.cuda.synchronize(self.device)
+                _cabi.lib().q4fc_fc_chain_destroy(h)
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 # ---- per-channel int8 weights ("Q8C") and the quantized embedding table ---------------------------------------------

@@ -19,6 +19,10 @@ Two schedules:
 ``glue="none"``   the 225 FCs alone, each reading the fp32 output of the one before (q, k, v and gate, up as one
     launch each): the FC-only chain that the per-token benchmark times.
 
+``chain=True`` runs the same schedule through ``llmops.FCChain``: one persistent launch per token (per layer and
+attention call when an ``attention`` callable is given) in which the weight stream does not stop between the FCs;
+the norms, the residual adds and silu * up are done by that kernel where it quantizes a step's input.
+
 There is no CPU path: every step is a call into the CUDA library.
 """
 from __future__ import annotations
@@ -36,7 +40,8 @@ class DecodeFCStack:
     def __init__(self, layers: list[dict], lm_head: torch.Tensor, *, hidden: int, intermediate: int, vocab: int,
                  rows: int = 1, glue: str = "llama", norms: list[dict] | None = None,
                  final_norm: torch.Tensor | None = None, eps: float = 1e-5,
-                 attention: Callable | None = None, graph: bool = True, tap: Callable | None = None) -> None:
+                 attention: Callable | None = None, graph: bool = True, tap: Callable | None = None,
+                 chain: bool = False) -> None:
         """``layers[i]``: packed weights under the keys q, k, v, o, gate, up, down.  ``norms[i]``: fp32 weights
         ``input`` and ``post`` of layer i's two rmsnorms (glue="llama"; default ones).  ``rows``: B*M <= 8.
         ``tap(name, layer, tensor)``: called after every step of the llama schedule with the buffer it wrote (for
@@ -81,6 +86,62 @@ class DecodeFCStack:
         self._graph = None
         self.use_graph = bool(graph)
         self.launches_per_token = (8 * len(layers) + 2) if glue == "llama" else (4 * len(layers) + 1)
+        self.chains = None
+        if chain:
+            if tap is not None:
+                raise RuntimeError("tap needs chain=False: a chain makes no Python calls between its steps")
+            self.chains = self._build_chains()
+            self.launches_per_token = len(self.chains)
+
+    # ------------------------------------------------------------------ the schedule as persistent launches
+    def _build_chains(self) -> list:
+        """The token's steps as ``FCChain`` objects: one for the whole token, or -- with an ``attention`` callable,
+        which runs between q, k, v and o -- one in front of every attention call and one behind the last."""
+        H, I, V = self.H, self.I, self.V
+        if self.glue == "none":
+            steps, h = [], self.x
+            for l in self.layers:
+                steps.append(dict(x=h, jobs=[(l["q"], H, self.q), (l["k"], H, self.k), (l["v"], H, self.v)]))
+                steps.append(dict(x=self.q, jobs=[(l["o"], H, self.h1)]))
+                steps.append(dict(x=self.h1, jobs=[(l["gate"], I, self.gate), (l["up"], I, self.up)]))
+                steps.append(dict(x=self.gate, jobs=[(l["down"], H, self.h2)]))
+                h = self.h2
+            steps.append(dict(x=h, jobs=[(self.lm_head, V, self.logits)]))
+            return [llmops.FCChain(steps)]
+        chains, steps, h = [], [], self.x
+        # the residual stream alternates between two buffers per half layer, so no step writes the buffer it reads
+        for i, (l, nw) in enumerate(zip(self.layers, self.norms)):
+            steps.append(dict(x=h, transform="rmsnorm", aux=nw["input"], eps=self.eps,
+                              jobs=[(l["q"], H, self.q), (l["k"], H, self.k), (l["v"], H, self.v)]))
+            a = self.q
+            if self.attention is not None:
+                chains.append(llmops.FCChain(steps))
+                steps, a = [], self.att
+            steps.append(dict(x=a, jobs=[(l["o"], H, self.h1, h)]))
+            steps.append(dict(x=self.h1, transform="rmsnorm", aux=nw["post"], eps=self.eps,
+                              jobs=[(l["gate"], I, self.gate), (l["up"], I, self.up)]))
+            steps.append(dict(x=self.gate, transform="silu_mul", aux=self.up, jobs=[(l["down"], H, self.h2, self.h1)]))
+            h = self.h2
+        steps.append(dict(x=h, transform="rmsnorm", aux=self.final_norm, eps=self.eps,
+                          jobs=[(self.lm_head, V, self.logits)]))
+        chains.append(llmops.FCChain(steps))
+        return chains
+
+    def _enqueue_chains(self) -> None:
+        if self.attention is None or self.glue == "none":
+            self.chains[0].run()
+            return
+        for i, c in enumerate(self.chains):
+            c.run()
+            if i < len(self.layers):
+                a = self.attention(self.q, self.k, self.v, i)
+                if a.data_ptr() != self.att.data_ptr():
+                    self.att.copy_(a, non_blocking=True)
+
+    def check(self) -> None:
+        """Raises if a bounded wait inside a chain launch ran out (host-synchronous)."""
+        for c in self.chains or []:
+            c.check()
 
     # ------------------------------------------------------------------ the schedule, enqueued on the current stream
     def _enqueue_llama(self) -> None:
@@ -120,7 +181,10 @@ class DecodeFCStack:
 
     def enqueue(self) -> None:
         """One token's schedule on the current stream (what the graph holds)."""
-        (self._enqueue_llama if self.glue == "llama" else self._enqueue_none)()
+        if self.chains is not None:
+            self._enqueue_chains()
+        else:
+            (self._enqueue_llama if self.glue == "llama" else self._enqueue_none)()
 
     # ------------------------------------------------------------------ a step
     def forward(self, x: torch.Tensor | None = None, sync: bool = False) -> torch.Tensor:
