@@ -457,8 +457,9 @@ __global__ void __launch_bounds__(kRThreads, 1) fc_decode_ring_kernel(const __gr
                     const int b = warp * NBLK + i;
                     if (b < nblk) {
                         const int ck = kb0 + b;
-                        block_accumulate<G, QTYPE, SIGNED>(q[i], wd[i], wm[i], my_codes + ck * G, row_live, sc + ck * 16,
-                                                           t, acc);
+                        // (one activation row: only row 2t of the lane's two rows is converted and scaled)
+                        block_accumulate<G, QTYPE, SIGNED, (ROWS == 1 ? 1 : 2)>(q[i], wd[i], wm[i], my_codes + ck * G,
+                                                                                row_live, sc + ck * 16, t, acc);
                     }
                 }
                 if (++cs_ == depth) cs_ = 0, fph ^= 1;
@@ -543,11 +544,11 @@ RingVariant* ring_variant_of() {
     return &v;
 }
 
-// The pre-quantized form has one instantiation per block type (nothing in it depends on the row count at
-// compile time)
+// The pre-quantized form has two instantiations per block type: one activation row (half the conversions and
+// scalings after the MMAs), and up to eight
 template <int G, int QTYPE, bool SIGNED, bool TP>
 RingVariant* ring_variant_for_rows(int rows, bool preq) {
-    if (preq) return ring_variant_of<G, QTYPE, SIGNED, 8, TP, true>();
+    if (preq) return rows <= 1 ? ring_variant_of<G, QTYPE, SIGNED, 1, TP, true>() : ring_variant_of<G, QTYPE, SIGNED, 8, TP, true>();
     if (rows <= 1) return ring_variant_of<G, QTYPE, SIGNED, 1, TP, false>();
     if (rows <= 2) return ring_variant_of<G, QTYPE, SIGNED, 2, TP, false>();
     if (rows <= 4) return ring_variant_of<G, QTYPE, SIGNED, 4, TP, false>();
