@@ -156,14 +156,17 @@ class HostFCGroup:
 
 
 class HostFCBatch:
-    """A fixed batch of independent host-buffer FCs with ONE copy each way per step: ``ys = batch(xs)``.
+    """A fixed batch of independent host-buffer FCs over ONE pinned staging block each way: ``ys = batch(xs)``.
 
     ``members``: tuples ``(wq, N, rows)`` -- packed weights resident on the GPU, output width, rows of that call's
-    input.  All inputs live back to back in one pinned host block and one device block, all outputs likewise, so
-    a step is: one host-to-device copy, the quantizers, the FCs (grouped into ``q4fc_fc_decode_batch`` launches
-    by row count), one device-to-host copy -- captured once as a CUDA graph and replayed.  ``x_staging(i)`` is
-    the pinned view ``[1, rows, K]`` of input i: writing activations straight into it saves the host-side copy.
-    Returns the pinned output views ``[1, rows, N]``, valid after ``sync`` (default: waited for here)."""
+    input.  All inputs live in one pinned host block and one device block, all outputs likewise; the calls are
+    grouped by row count into ``q4fc_fc_decode_batch`` launches, and the members of a launch lie back to back in the
+    blocks.  A step is a pipeline over the launches, largest row count first: its slice of the input block goes up
+    (one host-to-device copy per launch), its quantizers and its FC launch run, its slice of the output block comes
+    down (one device-to-host copy per launch) -- uploads, kernels and downloads of different launches overlap, and
+    the last download is the smallest.  Captured once as a CUDA graph and replayed.  ``x_staging(i)`` is the pinned
+    view ``[1, rows, K]`` of input i: writing activations straight into it saves the host-side copy.  Returns the
+    pinned output views ``[1, rows, N]``, valid after ``sync`` (default: waited for here)."""
 
     def __init__(self, members, *, graph: bool = True) -> None:
         self.members = [(wq, int(N), int(rows)) for wq, N, rows in members]
@@ -172,7 +175,9 @@ class HostFCBatch:
         dev = self.members[0][0].device
         self.device = dev
         self.stream = torch.cuda.Stream(dev)
-        self.side = torch.cuda.Stream(dev)
+        self.side = torch.cuda.Stream(dev)  # quantizers
+        self.up = torch.cuda.Stream(dev)    # host-to-device copies
+        self.down = torch.cuda.Stream(dev)  # device-to-host copies
         shapes = []
         for wq, N, rows in self.members:
             q, G = _cabi.infer_variant(wq.shape[2])
@@ -184,27 +189,30 @@ class HostFCBatch:
         self._y_host = torch.empty(ny, dtype=torch.float32).pin_memory()
         self._x_dev = torch.empty(nx, dtype=torch.float32, device=dev)
         self._y_dev = torch.empty(ny, dtype=torch.float32, device=dev)
-        self._xs_host, self._ys_host, xs_dev, ys_dev = [], [], [], []
-        ox = oy = 0
-        for r, K, N, _ in shapes:
-            self._xs_host.append(self._x_host[ox: ox + r * K].view(1, r, K))
-            xs_dev.append(self._x_dev[ox: ox + r * K].view(1, r, K))
-            self._ys_host.append(self._y_host[oy: oy + r * N].view(1, r, N))
-            ys_dev.append(self._y_dev[oy: oy + r * N].view(1, r, N))
-            ox, oy = ox + r * K, oy + r * N
-        self._xs_dev = xs_dev
-        self._xq = [llmops.QuantizedActivations(1, r, K, G, False, dev) for r, K, _, G in shapes]
-        # one launch per row count: calls of one launch then share the size of their code buffers
+        # one launch per row count (sixteen calls at most): calls of one launch share the size of their code buffers
         by_rows: dict = {}
         for i, (r, _, _, _) in enumerate(shapes):
             by_rows.setdefault(r, []).append(i)
-        self._groups = [idx for _, idx in sorted(by_rows.items())]
-        self._batches = []
-        for idx in self._groups:
-            for j in range(0, len(idx), 16):
-                part = idx[j: j + 16]
-                self._batches.append((part, llmops.FCBatch(
-                    [(self._xq[i], self.members[i][0], self.members[i][1], ys_dev[i]) for i in part], pdl=True)))
+        parts = []
+        for _, idx in sorted(by_rows.items(), reverse=True):
+            parts += [idx[j: j + 16] for j in range(0, len(idx), 16)]
+        n = len(shapes)
+        self._xs_host, self._ys_host, self._xs_dev, ys_dev = [None] * n, [None] * n, [None] * n, [None] * n
+        self._xq = [llmops.QuantizedActivations(1, r, K, G, False, dev) for r, K, _, G in shapes]
+        self._batches = []  # (members, FCBatch, slice of the input block, slice of the output block)
+        ox = oy = 0
+        for part in parts:
+            x0, y0 = ox, oy
+            for i in part:
+                r, K, N, _ = shapes[i]
+                self._xs_host[i] = self._x_host[ox: ox + r * K].view(1, r, K)
+                self._xs_dev[i] = self._x_dev[ox: ox + r * K].view(1, r, K)
+                self._ys_host[i] = self._y_host[oy: oy + r * N].view(1, r, N)
+                ys_dev[i] = self._y_dev[oy: oy + r * N].view(1, r, N)
+                ox, oy = ox + r * K, oy + r * N
+            fb = llmops.FCBatch([(self._xq[i], self.members[i][0], self.members[i][1], ys_dev[i]) for i in part],
+                                pdl=True)
+            self._batches.append((part, fb, slice(x0, ox), slice(y0, oy)))
         self.use_graph = bool(graph)
         self._graph = None
 
@@ -213,23 +221,32 @@ class HostFCBatch:
 
     def _enqueue(self) -> None:
         cur = torch.cuda.current_stream(self.device)
-        self._x_dev.copy_(self._x_host, non_blocking=True)
-        # quantizers on a side branch, group by group, so that all but the first group's hide behind the FCs
-        ready = torch.cuda.Event()
-        ready.record(cur)
-        self.side.wait_event(ready)
-        done = []
-        with torch.cuda.stream(self.side):
-            for part, _ in self._batches:
+        start = torch.cuda.Event()
+        start.record(cur)
+        for s in (self.up, self.side, self.down):
+            s.wait_event(start)
+        for part, fb, xs, ys in self._batches:
+            with torch.cuda.stream(self.up):
+                self._x_dev[xs].copy_(self._x_host[xs], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(self.up)
+            with torch.cuda.stream(self.side):
+                self.side.wait_event(arrived)
                 for i in part:
                     llmops.quantize_activations(self._xs_dev[i], self._shapes[i][3], out=self._xq[i])
-                ev = torch.cuda.Event()
-                ev.record(self.side)
-                done.append(ev)
-        for (part, fb), ev in zip(self._batches, done):
-            cur.wait_event(ev)
+                quantized = torch.cuda.Event()
+                quantized.record(self.side)
+            cur.wait_event(quantized)
             fb.run()
-        self._y_host.copy_(self._y_dev, non_blocking=True)
+            computed = torch.cuda.Event()
+            computed.record(cur)
+            with torch.cuda.stream(self.down):
+                self.down.wait_event(computed)
+                self._y_host[ys].copy_(self._y_dev[ys], non_blocking=True)
+        for s in (self.up, self.side, self.down):  # every branch joins the step's stream again
+            ev = torch.cuda.Event()
+            ev.record(s)
+            cur.wait_event(ev)
 
     def __call__(self, xs=None, sync: bool = True):
         if xs is not None:
