@@ -21,10 +21,12 @@ value  packed weight GB/s (packed bytes / time, 1 GB = 1e9 B: the reference's
 roofline  the dominant kernel (fc_decode_ring_kernel) alone: a second timed
        pass over the same FC launches with the inputs already quantized;
        achieved = algorithmic bytes per launch / average launch duration.
-       `per_call` lists every (shape, M) as a single call, in order, as
-       ops/perf_ops.py:190-245 measures it (rotating distinct weights).
-e2e    the same sweep through host.HostFCBatch: host buffers in and out, one
-       pinned block and one copy each way per step, inside the timed region.
+       `in_order_single_calls` has the 16 calls as 16 single launches in
+       order, and every (shape, M) by itself as ops/perf_ops.py:190-245
+       measures it (rotating distinct weights).
+e2e    the same sweep through host.HostFCBatch: host buffers in and out over
+       one pinned block each way, copies pipelined with the launches, inside
+       the timed region.
 
 With --gpus N > 1 every FC weight is split along N over the ranks (strong
 scaling: the job is the same sweep, each rank streams 1/N of every weight).
@@ -464,6 +466,25 @@ def our_arm(args) -> int:
             ms, _ = timed(capture(in_order), 200)
             per_call["sweep_in_order_pdl_ms" if pdl else "sweep_in_order_plain_ms"] = ms
         ms_in_order = per_call["sweep_in_order_pdl_ms"]
+        # every (shape, M) by itself: the same call repeated over enough distinct copies of the packed weights that
+        # none is found in L2 (at least 300 MB in turn), one graph of programmatic launches in order
+        table = {}
+        for K, N in SHAPES:
+            src = next(c for c in calls if c["K"] == K and c["N"] == N)
+            ncopies = max(2, -(-300_000_000 // packed_bytes(K, N)))
+            copies = [src["wq"]] + [src["wq"].clone() for _ in range(ncopies - 1)]
+            row = {}
+            for c in (c for c in calls if c["K"] == K and c["N"] == N):
+                def one_shape(c=c) -> None:
+                    for w in copies:
+                        ops.fc_Q4A(c["x"], w, N, out=c["y"], workspace=ws, pdl=True, path="decode")
+                ms, _ = timed(capture(one_shape), 20)
+                us = ms * 1e3 / ncopies
+                nb = algorithmic_bytes(K, N, c["M"])
+                row[f"M{c['M']}"] = {"us": us, "gb_s": nb / (us * 1e-6) / 1e9, "frac": nb / (us * 1e-6) / 1e9 / peak}
+            table[f"K{K}_N{N}"] = row
+            del copies
+        per_call["single_call_in_a_chain_of_its_own_kind"] = table
 
     # ---- end to end: host buffers in, host buffers out, one copy each way per step (public API)
     e2e = None

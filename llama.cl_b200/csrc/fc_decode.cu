@@ -40,6 +40,8 @@
 // a workspace slot per CTA plus an arrival counter per stripe, and the last
 // CTA to arrive adds the slots in CTA order.  There is no spin-wait anywhere
 // and the result does not depend on timing.
+#include <atomic>
+
 #include "common.cuh"
 #include "decode_math.cuh"
 
@@ -338,7 +340,7 @@ struct KernelEntry {
 
 template <int G, int QTYPE, bool SIGNED>
 int launch_variant(const DecodeParams& p, size_t smem, int grid, unsigned flags, cudaStream_t s) {
-    static bool attr_done[64] = {};
+    static std::atomic<bool> attr_done[64] = {};  // set once per device; a second setter repeats the same call
     int dev = 0;
     Q4FC_CUDA_OK(cudaGetDevice(&dev));
     auto* fn = fc_decode_kernel<G, QTYPE, SIGNED>;

@@ -32,6 +32,8 @@
 // freed and the kernel returns.
 #include <cuda.h>  // CUtensorMap and the cuTensorMapEncodeTiled prototype (resolved at run time, libcuda is not linked)
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace q4fc {
@@ -423,18 +425,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    // a function-local static is initialised once, also when several host threads arrive together
+    static const EncodeTiledFn fn = [] {
         void* sym = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
             qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-        else
-            cudaGetLastError();
-    }
+            return reinterpret_cast<EncodeTiledFn>(sym);
+        cudaGetLastError();
+        return static_cast<EncodeTiledFn>(nullptr);
+    }();
     return fn;
 }
 
@@ -463,7 +463,7 @@ int make_codes_map(CUtensorMap* map, const int8_t* codes, int64_t rows, int64_t 
 
 template <int G, int QTYPE, bool SIGNED>
 int launch_prefill_variant(const PrefillParams& p, const CUtensorMap& map, cudaStream_t s) {
-    static bool attr_done[64] = {};
+    static std::atomic<bool> attr_done[64] = {};  // set once per device; a second setter repeats the same call
     int dev = 0;
     Q4FC_CUDA_OK(cudaGetDevice(&dev));
     auto* fn = fc_prefill_kernel<G, QTYPE, SIGNED>;

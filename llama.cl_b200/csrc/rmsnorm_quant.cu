@@ -24,6 +24,8 @@
 //
 // One CTA per row: the row is first copied to shared memory by all warps, eight lanes run the chains, then
 // every warp quantizes 128-k chunks (one 512-byte read of shared memory each).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace q4fc {
@@ -160,7 +162,7 @@ int launch_rmsnorm_quant(const float* x, const float* residual, float* sum_out, 
     }
     const void* fn = (G == 32) ? reinterpret_cast<const void*>(&rmsnorm_quant_kernel<32>)
                                : reinterpret_cast<const void*>(&rmsnorm_quant_kernel<128>);
-    static bool attr_done[64][2] = {};
+    static std::atomic<bool> attr_done[64][2] = {};  // set once per device; a second setter repeats the same call
     int dev = 0;
     Q4FC_CUDA_OK(cudaGetDevice(&dev));
     if (smem > 48 * 1024 && (dev >= 64 || !attr_done[dev][G == 128])) {
