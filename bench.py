@@ -536,7 +536,7 @@ def our_arm(args) -> int:
         e2e = {"value": STEP_WEIGHT_BYTES / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "steps": n_e2e,
                "api": "host.HostFCBatch: one pinned block each way; per FC launch (row count) one copy up and one down, pipelined with the kernels" if not distributed else
-                      ("tp.HostFusedBatch: one pinned block and one copy each way per step, every rank" if fused
+                      ("tp.HostFusedBatch: one pinned block each way; per N-split launch one copy up and one down, pipelined with the kernels, every rank" if fused
                        else "TPLinearQ4 with explicit copies")}
         section_status("e2e")
 

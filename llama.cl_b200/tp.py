@@ -532,11 +532,13 @@ class HostFusedFC:
 
 
 class HostFusedBatch:
-    """``host.HostFCBatch`` over N-split weights: a fixed batch of independent host-buffer FCs with one copy each
-    way per step.  Every rank makes the same call with the same activations.  ``members``: ``(wq_shard, N, rows)``.
-    Per step: one host-to-device copy of all inputs, the quantizers, the step barrier, one
-    ``q4fc_fc_decode_tp_batch`` launch per group of up to four members of one row count, one unpacking launch
-    into the common output block, one device-to-host copy -- captured once as a CUDA graph and replayed."""
+    """``host.HostFCBatch`` over N-split weights: a fixed batch of independent host-buffer FCs over one pinned block
+    each way.  Every rank makes the same call with the same activations.  ``members``: ``(wq_shard, N, rows)``.
+    The members are grouped by row count into ``q4fc_fc_decode_tp_batch`` launches of up to four, largest row count
+    first; a step is the step barrier and then a pipeline over those launches: the launch's slice of the input block
+    goes up, its quantizers and the N-split launch run, one unpacking launch waits for the other ranks' columns of
+    its outputs, its slice of the output block comes down -- copies and kernels of different launches overlap.
+    Captured once as a CUDA graph and replayed."""
 
     def __init__(self, arena: TPArena, members, *, graph: bool = True) -> None:
         from . import llmops
@@ -547,7 +549,9 @@ class HostFusedBatch:
         dev = arena.device
         self.device = dev
         self.stream = torch.cuda.Stream(dev)
-        self.side = torch.cuda.Stream(dev)
+        self.side = torch.cuda.Stream(dev)  # quantizers
+        self.up = torch.cuda.Stream(dev)    # host-to-device copies
+        self.down = torch.cuda.Stream(dev)  # device-to-host copies
         self.layers = [FusedTPLinearQ4(self.schedule, wq, N, max_rows=rows, pdl=True) for wq, N, rows in self.members]
         shapes = [(rows, l.Kg * l.group_k, N, l.group_k) for (wq, N, rows), l in zip(self.members, self.layers)]
         self._shapes = shapes
@@ -557,23 +561,28 @@ class HostFusedBatch:
         self._y_host = torch.empty(ny, dtype=torch.float32).pin_memory()
         self._x_dev = torch.empty(nx, dtype=torch.float32, device=dev)
         self._y_dev = torch.empty(ny, dtype=torch.float32, device=dev)
-        self._xs_host, self._ys_host, self._xs_dev, self._ys_dev = [], [], [], []
-        ox = oy = 0
-        for r, K, N, _ in shapes:
-            self._xs_host.append(self._x_host[ox: ox + r * K].view(1, r, K))
-            self._xs_dev.append(self._x_dev[ox: ox + r * K].view(1, r, K))
-            self._ys_host.append(self._y_host[oy: oy + r * N].view(1, r, N))
-            self._ys_dev.append(self._y_dev[oy: oy + r * N].view(1, r, N))
-            ox, oy = ox + r * K, oy + r * N
-        self._xq = [llmops.QuantizedActivations(1, r, K, G, False, dev) for r, K, _, G in shapes]
         by_rows: dict = {}
         for i, (r, _, _, _) in enumerate(shapes):
             by_rows.setdefault(r, []).append(i)
-        self._batches = []
-        for _, idx in sorted(by_rows.items()):
-            for j in range(0, len(idx), 4):
-                part = idx[j: j + 4]
-                self._batches.append((part, FusedTPBatch([self.layers[i] for i in part], [self._xq[i] for i in part])))
+        parts = []
+        for _, idx in sorted(by_rows.items(), reverse=True):
+            parts += [idx[j: j + 4] for j in range(0, len(idx), 4)]
+        n = len(shapes)
+        self._xs_host, self._ys_host, self._xs_dev, self._ys_dev = [None] * n, [None] * n, [None] * n, [None] * n
+        self._xq = [llmops.QuantizedActivations(1, r, K, G, False, dev) for r, K, _, G in shapes]
+        self._batches = []  # (members, FusedTPBatch, slice of the input block, slice of the output block)
+        ox = oy = 0
+        for part in parts:
+            x0, y0 = ox, oy
+            for i in part:
+                r, K, N, _ = shapes[i]
+                self._xs_host[i] = self._x_host[ox: ox + r * K].view(1, r, K)
+                self._xs_dev[i] = self._x_dev[ox: ox + r * K].view(1, r, K)
+                self._ys_host[i] = self._y_host[oy: oy + r * N].view(1, r, N)
+                self._ys_dev[i] = self._y_dev[oy: oy + r * N].view(1, r, N)
+                ox, oy = ox + r * K, oy + r * N
+            fb = FusedTPBatch([self.layers[i] for i in part], [self._xq[i] for i in part])
+            self._batches.append((part, fb, slice(x0, ox), slice(y0, oy)))
         self.use_graph = bool(graph)
         self._graph = None
 
@@ -584,27 +593,33 @@ class HostFusedBatch:
         from . import llmops
 
         cur = torch.cuda.current_stream(self.device)
-        self._x_dev.copy_(self._x_host, non_blocking=True)
-        ready = torch.cuda.Event()
-        ready.record(cur)
-        self.side.wait_event(ready)
-        done = []
-        with torch.cuda.stream(self.side):
-            for part, _ in self._batches:
+        start = torch.cuda.Event()
+        start.record(cur)
+        for s in (self.up, self.side, self.down):
+            s.wait_event(start)
+        self.schedule.step_begin()
+        for part, fb, xs, ys in self._batches:
+            with torch.cuda.stream(self.up):
+                self._x_dev[xs].copy_(self._x_host[xs], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(self.up)
+            with torch.cuda.stream(self.side):
+                self.side.wait_event(arrived)
                 for i in part:
                     llmops.quantize_activations(self._xs_dev[i], self._shapes[i][3], out=self._xq[i])
-                ev = torch.cuda.Event()
-                ev.record(self.side)
-                done.append(ev)
-        self.schedule.step_begin()
-        outs, dsts = [], []
-        for (part, fb), ev in zip(self._batches, done):
+                quantized = torch.cuda.Event()
+                quantized.record(self.side)
+            cur.wait_event(quantized)
+            collect_many(fb.run(), [self._ys_dev[i] for i in part])
+            computed = torch.cuda.Event()
+            computed.record(cur)
+            with torch.cuda.stream(self.down):
+                self.down.wait_event(computed)
+                self._y_host[ys].copy_(self._y_dev[ys], non_blocking=True)
+        for s in (self.up, self.side, self.down):  # every branch joins the step's stream again
+            ev = torch.cuda.Event()
+            ev.record(s)
             cur.wait_event(ev)
-            outs += fb.run()
-            dsts += [self._ys_dev[i] for i in part]
-        for j in range(0, len(outs), 16):
-            collect_many(outs[j: j + 16], dsts[j: j + 16])
-        self._y_host.copy_(self._y_dev, non_blocking=True)
 
     def __call__(self, xs=None, sync: bool = True, check: bool = True):
         """``check`` (with ``sync``): read the status word after the step and raise if a bounded wait on another

@@ -222,6 +222,20 @@ def _fused_worker(rank, world, initfile, result_q):
                 y = hf(xh).clone()
                 want = pkg.llmops.fc_Q4A(xh.to(dev), full["up"], I).cpu()
                 expect(torch.allclose(y, want, rtol=1e-3, atol=1e-4), f"HostFusedFC step {step} M={M}")
+        # a fixed batch of host-buffer FCs over one pinned block each way (copies pipelined per launch), three row
+        # counts, five members in two of them: every output against the oracle, replayed with fresh inputs
+        mem = [("q", 1), ("up", 1), ("k", 3), ("q", 8), ("up", 8), ("k", 8), ("down", 8), ("last", 8)]
+        same = [m for m in mem if specs[m[0]][2:] == ("q4_1", 128)]  # one block type per batch object
+        hb = tp.HostFusedBatch(arena, [(tp.shard_packed(full[nm], world, rank), specs[nm][0], M) for nm, M in same])
+        for step in range(2):
+            xs = []
+            for i, (nm, M) in enumerate(same):
+                g = torch.Generator().manual_seed(900 + 20 * step + i)
+                xs.append(torch.randn(1, M, specs[nm][1], generator=g))
+            ys = hb(xs)
+            for (nm, M), xh, y in zip(same, xs, ys):
+                ref = torch.from_numpy(cpu.restated.fc(xh.numpy(), full_np[nm], specs[nm][0]))
+                expect(torch.allclose(y, ref, rtol=1e-3, atol=1e-4), f"HostFusedBatch {nm} M={M} step {step}")
         outs = chain(xg)  # and the first schedule is undisturbed by it
         torch.cuda.synchronize()
         verify(xg, outs, "after the solo schedule")
