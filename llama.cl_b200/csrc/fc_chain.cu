@@ -54,6 +54,7 @@ constexpr int kCW = 16;  // consumer warps
 constexpr int kCThreads = (kCW + 1) * 32;
 constexpr int kCRingMax = 10;
 constexpr int kCPartBufs = 4;
+constexpr int kChainAhead = 2;  // slots of the next step the producer requests before the consumers get there
 
 // The tables of a chain (a few KB) are copied into every CTA's shared memory at the start: a table read on the
 // critical path of a step then costs a shared-memory access, not an L2 round trip.
@@ -125,8 +126,11 @@ __device__ __forceinline__ void step_wait(const unsigned* counter, unsigned targ
 }
 
 // The consumer warps quantize the step's input rows (all K) into shared memory.  Item = one 128-k chunk of up to RI
-// rows; a warp loads NB items at once (one L2 round trip) and quantizes them as independent rows of one straight-
-// line call, so that their shuffle and divide chains overlap.  `scratch`: 64 floats nobody else uses meanwhile.
+// rows.  A warp works on CH items at a time as independent rows of one straight-line call (their shuffle and divide
+// chains overlap) and requests the next CH items before it starts on the present ones, so a step costs one L2 round
+// trip, not one per item.  The code is kept compact on purpose (one loop, no unrolling over items): it runs once per
+// step, cold, and a step's time is partly the time to fetch its instructions.  `scratch`: 64 floats nobody else
+// uses meanwhile.
 template <int G, int ROWS>
 __device__ __noinline__ void chain_quantize(const ChainStepDev* __restrict__ Sp, int rows, int warp, int lane,
                                             uint8_t* codes, float* sc, int code_stride, float* scratch) {
@@ -134,20 +138,20 @@ __device__ __noinline__ void chain_quantize(const ChainStepDev* __restrict__ Sp,
     constexpr int GPC = 128 / G;
     constexpr int RI = ROWS > 4 ? 4 : ROWS;
     constexpr int RGRP = ROWS / RI;  // 1 or 2: warp w always works on row group w % RGRP (kCW is even)
-    constexpr int NB = RI == 1 ? 6 : (RI == 2 ? 3 : 1);
-    const float* x = Sp->x;
+    constexpr int CH = RI == 1 ? 2 : 1;
+    const float* x = Sp->x;  // (shared memory: the CTA's copy of the table)
     const float* aux_p = Sp->aux;
-    const int64_t K = Sp->K, ldx = Sp->ldx;  // (shared memory: the CTA's copy of the table)
+    const int64_t K = Sp->K, ldx = Sp->ldx;
     const int Kg = Sp->Kg, transform = Sp->transform;
     const float eps = Sp->eps;
     const int chunks = (int)(((int64_t)Kg * G + 127) >> 7);
     const int items = chunks * RGRP;
     const int m0 = (warp % RGRP) * RI;
-    const bool single = items <= kCW * NB;  // every warp holds all of its items at once
+    const bool single = items <= kCW * CH;  // every warp holds all of its items at once
 
-    auto load = [&](float (&v)[NB][RI][4], float (&u)[NB][RI][4], int item0, bool with_aux) {
+    auto load = [&](float (&v)[CH][RI][4], float (&u)[CH][RI][4], int item0, bool with_aux) {
 #pragma unroll
-        for (int ib = 0; ib < NB; ib++) {
+        for (int ib = 0; ib < CH; ib++) {
             const int item = item0 + ib * kCW;
             const int64_t e = (int64_t)(item / RGRP) * 128 + lane * 4;
 #pragma unroll
@@ -170,7 +174,7 @@ __device__ __noinline__ void chain_quantize(const ChainStepDev* __restrict__ Sp,
         }
     };
 
-    float v[NB][RI][4], u[NB][RI][4];
+    float v[CH][RI][4], u[CH][RI][4];
     float r[RI];
 #pragma unroll
     for (int mm = 0; mm < RI; mm++) r[mm] = 0.0f;
@@ -182,10 +186,11 @@ __device__ __noinline__ void chain_quantize(const ChainStepDev* __restrict__ Sp,
         float ss[RI];
 #pragma unroll
         for (int mm = 0; mm < RI; mm++) ss[mm] = 0.0f;
-        for (int item0 = warp; item0 < items; item0 += kCW * NB) {
+#pragma unroll 1
+        for (int item0 = warp; item0 < items; item0 += kCW * CH) {
             load(v, u, item0, single);
 #pragma unroll
-            for (int ib = 0; ib < NB; ib++)
+            for (int ib = 0; ib < CH; ib++)
 #pragma unroll
                 for (int mm = 0; mm < RI; mm++)
 #pragma unroll
@@ -209,11 +214,15 @@ __device__ __noinline__ void chain_quantize(const ChainStepDev* __restrict__ Sp,
             r[mm] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(rms, eps)));
         }
     }
-    for (int item0 = warp; item0 < items; item0 += kCW * NB) {
-        if (transform != Q4FC_CHAIN_RMSNORM || !single) load(v, u, item0, true);
-        int lens[NB * RI];
+    if (!(transform == Q4FC_CHAIN_RMSNORM && single)) load(v, u, warp, true);
+#pragma unroll 1
+    for (int item0 = warp; item0 < items; item0 += kCW * CH) {
+        float vn[CH][RI][4], un[CH][RI][4];
+        const bool more = item0 + kCW * CH < items;
+        if (more) load(vn, un, item0 + kCW * CH, true);  // on its way while the present items are worked on
+        int lens[CH * RI];
 #pragma unroll
-        for (int ib = 0; ib < NB; ib++) {
+        for (int ib = 0; ib < CH; ib++) {
             const int item = item0 + ib * kCW;
             const int kbl = (item / RGRP) * GPC + lane / SEG;
             const int len = (item < items && kbl < Kg) ? (int)min((int64_t)G, K - (int64_t)kbl * G) : 0;
@@ -232,11 +241,11 @@ __device__ __noinline__ void chain_quantize(const ChainStepDev* __restrict__ Sp,
                 }
             }
         }
-        uint32_t packed[NB * RI];
-        float d[NB * RI], aux[NB * RI];
-        q8_quantize_rows_v<G, NB * RI, false>(reinterpret_cast<const float(&)[NB * RI][4]>(v), lane, lens, packed, d, aux);
+        uint32_t packed[CH * RI];
+        float d[CH * RI], aux[CH * RI];
+        q8_quantize_rows_v<G, CH * RI, false>(reinterpret_cast<const float(&)[CH * RI][4]>(v), lane, lens, packed, d, aux);
 #pragma unroll
-        for (int ib = 0; ib < NB; ib++) {
+        for (int ib = 0; ib < CH; ib++) {
             const int item = item0 + ib * kCW;
             const int ch = item / RGRP;
             const int kbl = ch * GPC + lane / SEG;
@@ -252,6 +261,14 @@ __device__ __noinline__ void chain_quantize(const ChainStepDev* __restrict__ Sp,
                     }
                 }
             }
+        }
+        if (more) {
+#pragma unroll
+            for (int ib = 0; ib < CH; ib++)
+#pragma unroll
+                for (int mm = 0; mm < RI; mm++)
+#pragma unroll
+                    for (int jj = 0; jj < 4; jj++) v[ib][mm][jj] = vn[ib][mm][jj], u[ib][mm][jj] = un[ib][mm][jj];
         }
     }
 }
@@ -281,6 +298,7 @@ __global__ void __launch_bounds__(kCThreads, 1) fc_chain_kernel(const __grid_con
     auto pfull_bar = [&](int b) { return bar0 + 256u + 8u * b; };
     auto pfree_bar = [&](int b) { return bar0 + 320u + 8u * b; };
     volatile int* fail = reinterpret_cast<volatile int*>(smem + 192);
+    volatile int* ready_step = reinterpret_cast<volatile int*>(smem + 200);  // steps whose input this CTA has quantized
     const ChainStepDev* steps = reinterpret_cast<const ChainStepDev*>(smem + 512);
     const ChainJobDev* jobs = reinterpret_cast<const ChainJobDev*>(smem + 512 + sizeof(ChainStepDev) * p.nsteps);
     float* part = reinterpret_cast<float*>(smem + p.part_off);
@@ -298,6 +316,7 @@ __global__ void __launch_bounds__(kCThreads, 1) fc_chain_kernel(const __grid_con
             mbar_init(pfree_bar(i), rows);
         }
         *fail = 0;
+        *ready_step = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -328,11 +347,27 @@ __global__ void __launch_bounds__(kCThreads, 1) fc_chain_kernel(const __grid_con
                 int a, b;
                 range(Sp->rot, Sp->stripes, a, b);
                 int jb = job0;
+                int ahead = 0;  // slots of this step issued before its input is quantized
                 for (int sg = a; sg < b; sg++) {
                     while (sg >= jobs[jb].s_end) jb++;
                     const int ls = sg - (jb > job0 ? jobs[jb - 1].s_end : 0);
                     const uint8_t* base = jobs[jb].wq + (int64_t)ls * Kg * BS;
                     for (int kb = 0; kb < Kg; kb += SB) {
+                        // No more than kChainAhead slots of a step are requested while the consumers are still on
+                        // their way to it: a ring-full of copies from every SM at once keeps HBM and the L2 queues
+                        // busy for microseconds, and the few loads and the counter traffic of the step change -- the
+                        // sequence that bounds a step -- would wait behind them.
+                        if (st > 0 && ahead >= kChainAhead && *ready_step < st) {
+                            const unsigned long long t0 = globaltimer_ns();
+                            for (unsigned it = 1; *ready_step < st && *fail == 0; it++) {
+                                __nanosleep(64);
+                                if ((it & 255) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+                                    *fail = 1;
+                                    atomicCAS(p.status, 0, 0x43524459);  // 'CRDY'
+                                }
+                            }
+                        }
+                        ahead++;
                         // a slot is reused once all consumer warps have taken their blocks out of it
                         if (!first) mbar_wait(empty_bar(s), eph, fail, p.status, 0x43454D50);  // 'CEMP'
                         const uint32_t bytes = (uint32_t)min(SB, Kg - kb) * BS;
@@ -374,6 +409,7 @@ __global__ void __launch_bounds__(kCThreads, 1) fc_chain_kernel(const __grid_con
             if (b <= a) continue;
             chain_quantize<G, ROWS>(Sp, rows, warp, lane, codes, sc, p.code_stride, part);
             asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory");
+            if (threadIdx.x == 0) *ready_step = st;  // the producer may now request the whole ring
 
             int jb = job0;
             for (int sg = a; sg < b; sg++, lc++) {
