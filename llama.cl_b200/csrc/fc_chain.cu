@@ -33,9 +33,9 @@
 // more (or none) differ from step to step.
 //
 // Step barrier.  Cooperative launch (all CTAs resident).  Every step has an arrival counter of its own in global
-// memory (one 128-byte line each), never reset: a CTA that has finished its stripes of step s (outputs stored, CTA
-// barrier) adds one with release semantics; a CTA that needs the outputs of step s polls the counter until it reaches
-// (launches so far + 1) x (CTAs with stripes in step s).  "Launches so far" is a word the last CTA to leave
+// memory (one 128-byte line each), never reset: the warp that stores a (stripe, row) of step s adds one with release
+// semantics right behind its stores; a CTA that needs the outputs of step s polls the counter until it reaches
+// (launches so far + 1) x (stripes x rows of step s).  "Launches so far" is a word the last CTA to leave
 // increments, so a handle can be launched again and again (and replayed from a CUDA graph) with nothing to reset.
 // Every wait -- this one and the mbarrier waits -- is bounded by one second of %globaltimer: when it runs out the
 // status word is set, the CTA's other waits end at once, all loops run to their ends and the kernel returns.  The
@@ -54,7 +54,7 @@ constexpr int kCW = 16;  // consumer warps
 constexpr int kCThreads = (kCW + 1) * 32;
 constexpr int kCRingMax = 10;
 constexpr int kCPartBufs = 4;
-constexpr int kChainAhead = 2;  // slots of the next step the producer requests before the consumers get there
+constexpr int kChainAhead = 4;  // slots of the next step the producer requests before the consumers get there
 
 // The tables of a chain (a few KB) are copied into every CTA's shared memory at the start: a table read on the
 // critical path of a step then costs a shared-memory access, not an L2 round trip.
@@ -74,7 +74,7 @@ struct ChainStepDev {
     int Kg;
     int job0, stripes;
     int rot;
-    int workers;  // CTAs that have stripes in this step
+    int units;  // arrivals a launch adds to the step's counter: its stripes x rows
     int pad;
 };
 static_assert(sizeof(ChainJobDev) % 8 == 0 && sizeof(ChainStepDev) % 8 == 0, "tables are copied as 8-byte words");
@@ -107,9 +107,9 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* a) {
     return v;
 }
 
-// One thread per CTA.  arrive: a release at GPU scope -- this CTA's outputs of the step (ordered before it by the
-// CTA barrier) are visible to whoever then reads the count with an acquire.  wait: until `target` CTAs have arrived
-// (wrap-safe comparison).  No fence.sc anywhere: the tables and weights an SM has cached stay cached.
+// arrive (one lane of the warp that stored the outputs, behind a __syncwarp): a release at GPU scope -- the warp's
+// stores are visible to whoever then reads the count with an acquire.  wait (one thread per CTA): until `target`
+// arrivals are in (wrap-safe comparison).  No fence.sc anywhere: the weights an SM has cached stay cached.
 __device__ __forceinline__ void step_arrive(unsigned* counter) {
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
 }
@@ -381,8 +381,7 @@ __global__ void __launch_bounds__(kCThreads, 1) fc_chain_kernel(const __grid_con
     } else {
         unsigned epoch = 0;  // launches of this handle completed before this one
         if (threadIdx.x == 0) epoch = ld_acquire_gpu(p.launches);
-        int prev_workers = 0;
-        bool worked = false;  // this CTA had stripes in the step before
+        int prev_units = 0;
         const uint8_t* my_codes = codes + g * p.code_stride + 8 * t;
         const bool row_live = g < rows;
         int cs_ = 0;       // ring position
@@ -390,23 +389,19 @@ __global__ void __launch_bounds__(kCThreads, 1) fc_chain_kernel(const __grid_con
         int lc = 0;        // stripes finished so far: turns the partial-sum buffers and the adding duty
         for (int st = 0; st < p.nsteps; st++) {
             const ChainStepDev* Sp = steps + st;
-            const int Kg = Sp->Kg, job0 = Sp->job0, workers = Sp->workers;
+            const int Kg = Sp->Kg, job0 = Sp->job0, units = Sp->units;
             int a, b;
             range(Sp->rot, Sp->stripes, a, b);
-            if (st > 0 && (worked || b > a)) {
-                // this CTA's outputs of the step before are complete (CTA barrier) and counted; before it reads the
-                // step's input, every CTA that had stripes in the step before has been counted
-                asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory");
-                if (threadIdx.x == 0) {
-                    unsigned* counter = p.arrivals + 32 * (st - 1);
-                    if (worked) step_arrive(counter);
-                    if (b > a) step_wait(counter, (epoch + 1u) * (unsigned)prev_workers, p, fail);
-                }
+            const int need = prev_units;
+            prev_units = units;
+            if (b <= a) continue;
+            if (st > 0) {
+                // before this CTA reads the step's input, every (stripe, row) of the step before has been stored and
+                // counted by the warp that stored it; the CTA barrier also says that all warps here are done with the
+                // codes of the step before
+                if (threadIdx.x == 0) step_wait(p.arrivals + 32 * (st - 1), (epoch + 1u) * (unsigned)need, p, fail);
                 asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory");
             }
-            prev_workers = workers;
-            worked = b > a;
-            if (b <= a) continue;
             chain_quantize<G, ROWS>(Sp, rows, warp, lane, codes, sc, p.code_stride, part);
             asm volatile("bar.sync 1, %0;" ::"n"(kCW * 32) : "memory");
             if (threadIdx.x == 0) *ready_step = st;  // the producer may now request the whole ring
@@ -490,6 +485,10 @@ __global__ void __launch_bounds__(kCThreads, 1) fc_chain_kernel(const __grid_con
                         if (J.addend != nullptr) sum = __fadd_rn(sum, addend);
                         J.y[m * J.ldy + n] = sum;
                     }
+                    // this (stripe, row) is out: counted with a release by the warp that stored it, so the count
+                    // costs nobody else a barrier and overlaps the other warps' work
+                    __syncwarp();
+                    if (lane == 0 && st + 1 < p.nsteps) step_arrive(p.arrivals + 32 * st);
                 }
             }
         }
@@ -602,7 +601,7 @@ int chain_create(const q4fc_chain_step* steps, int nsteps, const q4fc_fc_job* jo
             e.N = (int)j.N, e.ldy = (int)j.ldy, e.addend_ld = (int)j.ld_addend, e.s_end = (int)stripes;
         }
         d.stripes = (int)stripes;
-        d.workers = (int)(stripes < di->sm_count ? stripes : di->sm_count);
+        d.units = (int)stripes * rows;
         if (d.Kg > kg_max) kg_max = d.Kg;
     }
     if (jcur != njobs) {
