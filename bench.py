@@ -14,8 +14,9 @@ per step, four times the L2), so no call finds its weights in cache.  Weights
 value  packed weight GB/s (packed bytes / time, 1 GB = 1e9 B: the reference's
        own "Bound: GB/s" figure of ops/perf_ops.py:243-245), inputs (fp32
        activations, packed weights) resident in HBM.  The 16 calls of a step
-       are independent, so a step quantizes the 16 inputs and runs the FCs as
-       four launches of q4fc_fc_decode_batch (one per row count), replayed as
+       are independent, so a step quantizes the 16 inputs (four launches of
+       q4fc_quant_x_q8_batch) and runs the FCs as four launches of
+       q4fc_fc_decode_batch (one per row count each), replayed as
        one CUDA graph.  The timed region runs every step `inner` times so that
        it lasts about half a second; ms_per_step is per single step.
 roofline  the dominant kernel (fc_decode_ring_kernel) alone: a second timed
@@ -360,11 +361,12 @@ def our_arm(args) -> int:
         # one launch per row count: calls of a launch then share the size of their code buffers
         groups = [[c for c in calls if c["M"] == M] for M in MS]
         batches = [ops.FCBatch([(c["xq"], c["wq"], c["N"], c["y"]) for c in g_], pdl=True) for g_ in groups]
+        qbatches = [ops.QuantizeBatch([(c["x"], c["xq"]) for c in g_]) for g_ in groups]
         n_fc_launches = len(batches)
         side = torch.cuda.Stream(dev)
 
         def step_device() -> None:
-            # the quantizers run on a side branch of the graph, group by group: all but the first group's hide
+            # the quantizers (one launch per group) run on a side branch of the graph: all but the first group's hide
             # behind the FCs of the group before
             cur = torch.cuda.current_stream(dev)
             start = torch.cuda.Event()
@@ -372,9 +374,8 @@ def our_arm(args) -> int:
             side.wait_event(start)
             done = []
             with torch.cuda.stream(side):
-                for g_ in groups:
-                    for c in g_:
-                        ops.quantize_activations(c["x"], GROUP_K, out=c["xq"])
+                for qb in qbatches:
+                    qb.run()  # the group's four quantizers as one launch
                     ev = torch.cuda.Event()
                     ev.record(side)
                     done.append(ev)
@@ -386,10 +387,11 @@ def our_arm(args) -> int:
             for b in batches:
                 b.run()
 
-        launches_per_step = len(calls) + len(batches)
+        launches_per_step = len(qbatches) + len(batches)
     elif fused:
         groups = [[c for c in calls if c["M"] == M] for M in MS]
         tbatches = [tp.FusedTPBatch([c["layer"] for c in g_], [c["xq"] for c in g_]) for g_ in groups]
+        qbatches = [ops.QuantizeBatch([(c["x"], c["xq"]) for c in g_]) for g_ in groups]
         side = torch.cuda.Stream(dev)
 
         def step_device() -> None:
@@ -402,9 +404,8 @@ def our_arm(args) -> int:
             side.wait_event(start)
             done = []
             with torch.cuda.stream(side):
-                for g_ in groups:
-                    for c in g_:
-                        ops.quantize_activations(c["x"], GROUP_K, out=c["xq"])
+                for qb in qbatches:
+                    qb.run()  # the group's four quantizers as one launch
                     ev = torch.cuda.Event()
                     ev.record(side)
                     done.append(ev)
@@ -417,7 +418,7 @@ def our_arm(args) -> int:
 
         step_fc_only = step_device
         n_fc_launches = len(tbatches)
-        launches_per_step = len(calls) + len(tbatches) + 2  # quantizers, N-split launches, step barrier, unpacking
+        launches_per_step = len(qbatches) + len(tbatches) + 2  # quantizers, N-split launches, step barrier, unpacking
     else:
         def step_device() -> None:
             for c in calls:
@@ -833,9 +834,9 @@ def our_arm(args) -> int:
                     f"N-split tp{world}, columns stored into every rank's buffer by the FC kernel (epoch-stamped "
                     f"64-bit words, NVLink peer stores)" if fused else f"N-split tp{world} + NCCL all-gather"),
                 **({"tp_note": tp_note} if tp_note else {}),
-                "step": ("cuda graph: 16 quantizer launches on a side branch + 4 launches of q4fc_fc_decode_batch "
+                "step": ("cuda graph: 4 quantizer launches (q4fc_quant_x_q8_batch, one per row count) on a side branch + 4 launches of q4fc_fc_decode_batch "
                          "(one per row count)" if not distributed else
-                         "cuda graph: step barrier, 16 quantizer launches on a side branch, 4 launches of "
+                         "cuda graph: step barrier, 4 quantizer launches (one per row count) on a side branch, 4 launches of "
                          "q4fc_fc_decode_tp_batch (one per row count), one unpacking launch" if fused else "eager"),
                 "inner_repeats_per_step": inner, "timed_region_ms": ms_outer * args.steps},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps * inner,

@@ -215,6 +215,17 @@ int q4fc_fc_decode_batch(const q4fc_fc_call* calls, int ncalls, int qtype, int g
 size_t q4fc_xq_bytes(int64_t rows, int64_t K, int group_k);
 int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int group_k, int want_isum, void* xq,
                     unsigned flags, q4fc_stream_t stream);
+/* q4fc_quant_x_q8 for up to 16 inputs in ONE launch (the inputs of a batch of independent FCs): the same codes,
+ * scales and sums as one call per input.  All inputs share group_k and want_isum. */
+typedef struct q4fc_xq_call {
+    const float* x; /* fp32 [rows][ldx] */
+    int64_t rows;   /* <= 8 */
+    int64_t K;
+    int64_t ldx;
+    void* xq;       /* q4fc_xq_bytes(rows, K, group_k) bytes, 256-byte aligned */
+} q4fc_xq_call;
+int q4fc_quant_x_q8_batch(const q4fc_xq_call* calls, int ncalls, int group_k, int want_isum, unsigned flags,
+                          q4fc_stream_t stream);
 int q4fc_rmsnorm_quant(const float* x, int64_t rows, int64_t K, int64_t ldx, const float* weight, float eps, float* y,
                        int64_t ldy, int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream);
 int q4fc_add_rmsnorm_quant(const float* x, const float* residual, float* sum_out, int64_t rows, int64_t K, int64_t ldx,

@@ -27,7 +27,7 @@ SYMBOLS = (
     "q4fc_tp_step_begin", "q4fc_tp_collect", "q4fc_fc_decode_tp", "q4fc_tp_site_bytes",
     "q4fc_fc_decode_tp_batch", "q4fc_tp_collect_multi",
     "q4fc_xq_bytes", "q4fc_quant_x_q8", "q4fc_rmsnorm_quant", "q4fc_add_rmsnorm_quant", "q4fc_fc_decode_q8",
-    "q4fc_silu_mul_quant",
+    "q4fc_silu_mul_quant", "q4fc_quant_x_q8_batch",
     "q4fc_fc_chain_create", "q4fc_fc_chain_run", "q4fc_fc_chain_check", "q4fc_fc_chain_destroy",
     "q4fc_q8c_pack", "q4fc_q8c_workspace_bytes", "q4fc_q8c_fc", "q4fc_emb_q8c_quant", "q4fc_emb_q8c",
 )
@@ -74,6 +74,11 @@ class ChainStep(C.Structure):
 
 
 CHAIN_PLAIN, CHAIN_RMSNORM, CHAIN_SILU_MUL = 0, 1, 2
+
+
+class XqCall(C.Structure):
+    """``q4fc_xq_call`` of include/q4fc_b200.h."""
+    _fields_ = [("x", C.c_void_p), ("rows", C.c_int64), ("K", C.c_int64), ("ldx", C.c_int64), ("xq", C.c_void_p)]
 
 
 class TpCall(C.Structure):
@@ -145,6 +150,7 @@ def lib() -> C.CDLL:
     L.q4fc_xq_bytes.restype = sz
     L.q4fc_xq_bytes.argtypes = [i64, i64, i32]
     L.q4fc_quant_x_q8.argtypes = [vp, i64, i64, i64, i32, i32, vp, u32, vp]
+    L.q4fc_quant_x_q8_batch.argtypes = [C.POINTER(XqCall), i32, i32, i32, u32, vp]
     L.q4fc_rmsnorm_quant.argtypes = [vp, i64, i64, i64, vp, f32, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_add_rmsnorm_quant.argtypes = [vp, vp, vp, i64, i64, i64, vp, f32, vp, i64, i32, i32, vp, u32, vp]
     L.q4fc_silu_mul_quant.argtypes = [vp, vp, i64, i64, i64, vp, i64, i32, i32, vp, u32, vp]

@@ -285,6 +285,24 @@ int q4fc_quant_x_q8(const float* x, int64_t rows, int64_t K, int64_t ldx, int gr
                               (flags & Q4FC_FLAG_PDL) != 0, static_cast<cudaStream_t>(stream));
 }
 
+int q4fc_quant_x_q8_batch(const q4fc_xq_call* calls, int ncalls, int group_k, int want_isum, unsigned flags,
+                          q4fc_stream_t stream) {
+    if (ncalls < 0 || ncalls > 16 || (ncalls > 0 && !calls)) {
+        set_error("quant_x_q8_batch: ncalls=%d outside 0..16, or null calls", ncalls);
+        return Q4FC_ELIMIT;
+    }
+    for (int i = 0; i < ncalls; i++) {
+        const q4fc_xq_call& c = calls[i];
+        if (int rc = check_xq_args("quant_x_q8_batch", c.rows, c.K, group_k, c.xq)) return rc;
+        if (c.rows > 0 && (!c.x || c.ldx < c.K || !aligned(c.x, 4))) {
+            set_error("quant_x_q8_batch: call %d: null or misaligned x, or ldx < K", i);
+            return Q4FC_EINVAL;
+        }
+    }
+    return launch_quant_x_pre_batch(calls, ncalls, group_k, want_isum != 0, (flags & Q4FC_FLAG_PDL) != 0,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int q4fc_silu_mul_quant(const float* gate, const float* up, int64_t rows, int64_t K, int64_t ld, float* prod, int64_t ldp,
                         int group_k, int want_isum, void* xq, unsigned flags, q4fc_stream_t stream) {
     if (int rc = check_xq_args("silu_mul_quant", rows, K, group_k, xq)) return rc;

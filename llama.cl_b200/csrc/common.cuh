@@ -83,6 +83,7 @@ size_t quant_pre_bytes(int64_t rows, int64_t K, int G);
 int launch_quant_x_pre(const float* x, int rows, int64_t K, int64_t ldx, int G, bool want_isum, int8_t* codes,
                        float* sc, bool pdl, cudaStream_t s, const float* up = nullptr, float* prod = nullptr,
                        int64_t ldp = 0);
+int launch_quant_x_pre_batch(const q4fc_xq_call* calls, int n, int G, bool want_isum, bool pdl, cudaStream_t s);
 // the same kernel with outputs stored, epoch-stamped, into every rank's buffer (tp->y_peer)
 int launch_fc_decode_ring_tp(const float* x, int rows, int64_t K, int64_t ldx, const uint8_t* wq, int64_t Ng,
                                 int64_t Kg, int qtype, int G, int64_t N, int64_t ldy, unsigned flags, cudaStream_t s,

@@ -126,16 +126,14 @@ __global__ void __launch_bounds__(kQxWarps * 32) quant_x_kernel(const float* __r
 // degree-5 polynomial and the reciprocal by _mm256_rcp_ps (relative error up to 3.7e-4), so the products agree
 // with it to about 4e-4 relative, inside the 1e-3 / 1e-4 output tolerance, not bit for bit.
 template <int G>
-__global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restrict__ x, int rows, int64_t K,
-                                                          int64_t ldx, int64_t Kg, int vec_ok, int want_isum,
-                                                          int early_release, int8_t* __restrict__ codes,
-                                                          float* __restrict__ sc, const float* __restrict__ up,
-                                                          float* __restrict__ prod, int64_t ldp) {
+__device__ __forceinline__ void quant_pre_unit(const float* __restrict__ x, int rows, int64_t K, int64_t ldx, int64_t Kg,
+                                               int vec_ok, int want_isum, int early_release, int8_t* __restrict__ codes,
+                                               float* __restrict__ sc, const float* __restrict__ up,
+                                               float* __restrict__ prod, int64_t ldp, int64_t unit) {
     constexpr int SEG = G / 4;
     constexpr int GPC = 128 / G;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31;
     const int64_t chunks = (Kg * G + 127) / 128;
-    const int64_t unit = (int64_t)blockIdx.x * 4 + warp;
     // In a chain of programmatic launches the FC kernel behind this one should start as early as it can:
     // its start-up then runs beside the FC before.
     if (early_release) pdl_launch_dependents();
@@ -231,7 +229,83 @@ __global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restric
     }
 }
 
+template <int G>
+__global__ void __launch_bounds__(128) quant_x_pre_kernel(const float* __restrict__ x, int rows, int64_t K,
+                                                          int64_t ldx, int64_t Kg, int vec_ok, int want_isum,
+                                                          int early_release, int8_t* __restrict__ codes,
+                                                          float* __restrict__ sc, const float* __restrict__ up,
+                                                          float* __restrict__ prod, int64_t ldp) {
+    quant_pre_unit<G>(x, rows, K, ldx, Kg, vec_ok, want_isum, early_release, codes, sc, up, prod, ldp,
+                      (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5));
+}
+
+// Several inputs in one launch (a batch of independent FCs has as many inputs to quantize, and each launch of its own
+// would cost more than its work): the warps of the grid are dealt out to the inputs in order.
+constexpr int kMaxQuantBatch = 16;
+struct QuantBatch {
+    const float* x[kMaxQuantBatch];
+    int8_t* codes[kMaxQuantBatch];
+    float* sc[kMaxQuantBatch];
+    int64_t K[kMaxQuantBatch], ldx[kMaxQuantBatch];
+    int rows[kMaxQuantBatch], vec_ok[kMaxQuantBatch];
+    int unit0[kMaxQuantBatch + 1];  // first warp of input i; [n] = warps in all
+    int n;
+};
+template <int G>
+__global__ void __launch_bounds__(128) quant_x_pre_batch_kernel(const __grid_constant__ QuantBatch b, int want_isum,
+                                                                int early_release) {
+    const int unit = (int)blockIdx.x * 4 + (threadIdx.x >> 5);
+    int i = 0;
+    while (i + 1 < b.n && unit >= b.unit0[i + 1]) i++;
+    const int64_t Kg = (b.K[i] + G - 1) / G;
+    if (unit >= b.unit0[b.n]) {
+        if (early_release) pdl_launch_dependents();
+        return;
+    }
+    quant_pre_unit<G>(b.x[i], b.rows[i], b.K[i], b.ldx[i], Kg, b.vec_ok[i], want_isum, early_release, b.codes[i], b.sc[i],
+                      nullptr, nullptr, 0, (int64_t)(unit - b.unit0[i]));
+}
+
 }  // namespace
+
+int launch_quant_x_pre_batch(const q4fc_xq_call* calls, int n, int G, bool want_isum, bool pdl, cudaStream_t s) {
+    QuantBatch b = {};
+    int units = 0;
+    for (int i = 0; i < n; i++) {
+        const q4fc_xq_call& c = calls[i];
+        if (c.rows == 0) continue;
+        const int64_t Kg = (c.K + G - 1) / G;
+        const int64_t chunks = (Kg * G + 127) / 128;
+        uint8_t* base = static_cast<uint8_t*>(c.xq);
+        const int k = b.n++;
+        b.x[k] = c.x, b.rows[k] = (int)c.rows, b.K[k] = c.K, b.ldx[k] = c.ldx;
+        b.codes[k] = reinterpret_cast<int8_t*>(base);
+        b.sc[k] = reinterpret_cast<float*>(base + align_up((size_t)(c.rows * Kg * G), 256));
+        b.vec_ok[k] = (c.K % 4 == 0) && (c.ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(c.x) & 15) == 0);
+        b.unit0[k] = units;
+        if (chunks * c.rows > 0x3fffffff - units) {
+            set_error("quant_x_q8_batch: too many values for one launch");
+            return Q4FC_ELIMIT;
+        }
+        units += (int)(chunks * c.rows);
+    }
+    if (b.n == 0) return Q4FC_OK;
+    b.unit0[b.n] = units;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((units + 3) / 4));
+    cfg.blockDim = dim3(128);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    if (G == 32)
+        Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_batch_kernel<32>, b, (int)want_isum, (int)pdl));
+    else
+        Q4FC_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_x_pre_batch_kernel<128>, b, (int)want_isum, (int)pdl));
+    return Q4FC_OK;
+}
 
 size_t quant_pre_bytes(int64_t rows, int64_t K, int G) {
     const int64_t Kg = (K + G - 1) / G;

@@ -212,7 +212,8 @@ class HostFCBatch:
                 ox, oy = ox + r * K, oy + r * N
             fb = llmops.FCBatch([(self._xq[i], self.members[i][0], self.members[i][1], ys_dev[i]) for i in part],
                                 pdl=True)
-            self._batches.append((part, fb, slice(x0, ox), slice(y0, oy)))
+            qb = llmops.QuantizeBatch([(self._xs_dev[i], self._xq[i]) for i in part])  # the launch's quantizers as one
+            self._batches.append((part, fb, slice(x0, ox), slice(y0, oy), qb))
         self.use_graph = bool(graph)
         self._graph = None
 
@@ -225,15 +226,14 @@ class HostFCBatch:
         start.record(cur)
         for s in (self.up, self.side, self.down):
             s.wait_event(start)
-        for part, fb, xs, ys in self._batches:
+        for part, fb, xs, ys, qb in self._batches:
             with torch.cuda.stream(self.up):
                 self._x_dev[xs].copy_(self._x_host[xs], non_blocking=True)
                 arrived = torch.cuda.Event()
                 arrived.record(self.up)
             with torch.cuda.stream(self.side):
                 self.side.wait_event(arrived)
-                for i in part:
-                    llmops.quantize_activations(self._xs_dev[i], self._shapes[i][3], out=self._xq[i])
+                qb.run()
                 quantized = torch.cuda.Event()
                 quantized.record(self.side)
             cur.wait_event(quantized)

@@ -24,7 +24,7 @@ from ._cabi import FLAG_NIBBLE_SIGNED, FLAG_PDL, FLAG_STREAMK, Q4_0, Q4_1
 
 __all__ = ["offline_FC_quant_Q4A", "offline_FC_dequant_Q4A", "fc_Q4A", "FC_dynamic_quantize_x",
            "fc_workspace", "Workspace", "fc_Q4A_multi", "FCBatch", "fc_Q4A_q8", "quantize_activations", "rmsnorm_quantize", "silu_mul_quantize",
-           "QuantizedActivations", "FCChain", "FC_quant_Q8C", "FC_evaluate_Q8C", "embedding_q8c_quant_w", "embedding_q8c", "check_device_status"]
+           "QuantizedActivations", "QuantizeBatch", "FCChain", "FC_quant_Q8C", "FC_evaluate_Q8C", "embedding_q8c_quant_w", "embedding_q8c", "check_device_status"]
 
 
 def _stream_ptr(device: torch.device) -> int:
@@ -254,6 +254,35 @@ def quantize_activations(input: torch.Tensor, group_k: int, *, nibble_signed: bo
                                                 xq.buf.data_ptr(), FLAG_PDL if pdl else 0,
                                                 _stream_ptr(input.device)), "quantize_activations")
     return xq
+
+
+class QuantizeBatch:
+    """``quantize_activations`` for up to 16 (input, output) pairs as ONE launch (``q4fc_quant_x_q8_batch``).  The
+    argument block is built once; ``run()`` only launches (capturable in a CUDA graph)."""
+
+    def __init__(self, pairs, *, pdl: bool = False) -> None:
+        if not 1 <= len(pairs) <= 16:
+            raise RuntimeError("QuantizeBatch: one to sixteen inputs")
+        self.n = len(pairs)
+        self._args = (_cabi.XqCall * self.n)()
+        self._keep = list(pairs)
+        G = signed = None
+        for i, (x, xq) in enumerate(pairs):
+            _require_cuda(x, f"pairs[{i}] input", torch.float32, 3)
+            if not isinstance(xq, QuantizedActivations) or (xq.B, xq.M, xq.K) != tuple(x.shape):
+                raise RuntimeError(f"pairs[{i}]: the QuantizedActivations do not fit the input {tuple(x.shape)}")
+            if G is None:
+                G, signed, self.device = xq.group_k, xq.signed, x.device
+            elif (xq.group_k, xq.signed) != (G, signed):
+                raise RuntimeError("QuantizeBatch: the outputs differ in group size or signedness")
+            a = self._args[i]
+            a.x, a.rows, a.K, a.ldx, a.xq = x.data_ptr(), xq.rows, xq.K, xq.K, xq.buf.data_ptr()
+        self.group_k, self.signed, self.flags = G, signed, (FLAG_PDL if pdl else 0)
+
+    def run(self) -> None:
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.lib().q4fc_quant_x_q8_batch(self._args, self.n, self.group_k, int(self.signed), self.flags,
+                                                          _stream_ptr(self.device)), "quant_x_q8_batch")
 
 
 def rmsnorm_quantize(input: torch.Tensor, weight: torch.Tensor, eps: float, group_k: int, *,

@@ -582,7 +582,8 @@ class HostFusedBatch:
                 self._ys_dev[i] = self._y_dev[oy: oy + r * N].view(1, r, N)
                 ox, oy = ox + r * K, oy + r * N
             fb = FusedTPBatch([self.layers[i] for i in part], [self._xq[i] for i in part])
-            self._batches.append((part, fb, slice(x0, ox), slice(y0, oy)))
+            qb = llmops.QuantizeBatch([(self._xs_dev[i], self._xq[i]) for i in part])  # the launch's quantizers as one
+            self._batches.append((part, fb, slice(x0, ox), slice(y0, oy), qb))
         self.use_graph = bool(graph)
         self._graph = None
 
@@ -598,15 +599,14 @@ class HostFusedBatch:
         for s in (self.up, self.side, self.down):
             s.wait_event(start)
         self.schedule.step_begin()
-        for part, fb, xs, ys in self._batches:
+        for part, fb, xs, ys, qb in self._batches:
             with torch.cuda.stream(self.up):
                 self._x_dev[xs].copy_(self._x_host[xs], non_blocking=True)
                 arrived = torch.cuda.Event()
                 arrived.record(self.up)
             with torch.cuda.stream(self.side):
                 self.side.wait_event(arrived)
-                for i in part:
-                    llmops.quantize_activations(self._xs_dev[i], self._shapes[i][3], out=self._xq[i])
+                qb.run()
                 quantized = torch.cuda.Event()
                 quantized.record(self.side)
             cur.wait_event(quantized)

@@ -278,3 +278,26 @@ def test_streamk_counts_the_stripes_of_the_packed_tensor(pkg, oracle):
     assert L.q4fc_fc_decode_noalloc(*args2, 0, s) == 0, L.q4fc_last_error()
     torch.cuda.synchronize()
     assert close(got.cpu().numpy(), want)
+
+
+def test_quantize_batch_equals_single_launches(pkg):
+    """q4fc_quant_x_q8_batch: several inputs quantized by one launch -- codes, scales and sums bit-equal to one
+    q4fc_quant_x_q8 launch per input, for both group sizes, ragged K and different row counts."""
+    ops = pkg.llmops
+    g = torch.Generator().manual_seed(31)
+    for G in (32, 128):
+        xs = [torch.randn(1, M, K, generator=g).cuda() for M, K in ((1, 4096), (8, 11008), (3, 72), (2, 1000), (5, 128))]
+        outs = [ops.QuantizedActivations(1, x.shape[1], x.shape[2], G, False, x.device) for x in xs]
+        for o in outs:
+            o.buf.fill_(0x55)
+        qb = ops.QuantizeBatch(list(zip(xs, outs)))
+        qb.run()
+        for x, o in zip(xs, outs):
+            ref = ops.quantize_activations(x, G)
+            assert torch.equal(o.codes(), ref.codes())
+            a, b = o.scales_and_sums(), ref.scales_and_sums()
+            assert all(torch.equal(p, q) for p, q in zip(a, b)) if isinstance(a, (tuple, list)) else torch.equal(a, b)
+    with pytest.raises(RuntimeError):
+        ops.QuantizeBatch([])
+    with pytest.raises(RuntimeError):
+        ops.QuantizeBatch([(xs[0], outs[1])])  # shapes do not fit
