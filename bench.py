@@ -359,7 +359,7 @@ def our_arm(args) -> int:
     n_fc_launches = len(calls)
     if not distributed:
         # one launch per row count: calls of a launch then share the size of their code buffers
-        groups = [[c for c in calls if c["M"] == M] for M in MS]
+        groups = [[c for c in calls if c["M"] == M] for M in reversed(MS)]  # largest first: the step ends on the smallest launch
         batches = [ops.FCBatch([(c["xq"], c["wq"], c["N"], c["y"]) for c in g_], pdl=True) for g_ in groups]
         qbatches = [ops.QuantizeBatch([(c["x"], c["xq"]) for c in g_]) for g_ in groups]
         n_fc_launches = len(batches)
@@ -389,7 +389,7 @@ def our_arm(args) -> int:
 
         launches_per_step = len(qbatches) + len(batches)
     elif fused:
-        groups = [[c for c in calls if c["M"] == M] for M in MS]
+        groups = [[c for c in calls if c["M"] == M] for M in reversed(MS)]  # largest first: the step ends on the smallest launch
         tbatches = [tp.FusedTPBatch([c["layer"] for c in g_], [c["xq"] for c in g_]) for g_ in groups]
         qbatches = [ops.QuantizeBatch([(c["x"], c["xq"]) for c in g_]) for g_ in groups]
         side = torch.cuda.Stream(dev)
