@@ -50,7 +50,6 @@ namespace {
 
 constexpr int kDecWarps = 8;
 constexpr int kDecThreads = kDecWarps * 32;
-constexpr uint32_t kNibMask = 0x0F0F0F0Fu;
 
 struct DecodeParams {
     const float* x;
@@ -213,46 +212,9 @@ __global__ void __launch_bounds__(kDecThreads, 2) fc_decode_kernel(const DecodeP
     #pragma unroll
         for (int i = 0; i < NBLK; i++) {
             if (b + i < wb1) {
-                int ia[4] = {0, 0, 0, 0}, ib[4] = {0, 0, 0, 0};
-    #pragma unroll
-                for (int j = 0; j < SETS; j++) {
-                    uint2 xb = make_uint2(0u, 0u);
-                    if (row_live) xb = *reinterpret_cast<const uint2*>(my_codes + (int64_t)kb * G + 32 * j);
-                    const uint4 q = st.q[i][j];
-                    uint32_t l0 = q.x & kNibMask, l1 = q.y & kNibMask, l2 = q.z & kNibMask, l3 = q.w & kNibMask;
-                    uint32_t h0 = (q.x >> 4) & kNibMask, h1 = (q.y >> 4) & kNibMask, h2 = (q.z >> 4) & kNibMask,
-                             h3 = (q.w >> 4) & kNibMask;
-                    if (SIGNED) {
-                        l0 ^= 0x08080808u, l1 ^= 0x08080808u, l2 ^= 0x08080808u, l3 ^= 0x08080808u;
-                        h0 ^= 0x08080808u, h1 ^= 0x08080808u, h2 ^= 0x08080808u, h3 ^= 0x08080808u;
-                    }
-                    mma_u8s8(ia, l0, l1, h0, h1, xb.x, xb.y);
-                    mma_u8s8(ib, l2, l3, h2, h3, xb.x, xb.y);
-                }
-                // per-group scaling; lane holds columns 4g..4g+3 for rows 2t, 2t+1
-                const float4 s4 = *reinterpret_cast<const float4*>(sc + kb * 16 + t * 4);  // xs0, gs0, xs1, gs1
-                const float2 wd01 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].x));
-                const float2 wd23 = __half22float2(*reinterpret_cast<const __half2*>(&st.wd[i].y));
-                const float wdf[4] = {wd01.x, wd01.y, wd23.x, wd23.y};
-                const int iv[4][2] = {{ia[0], ia[1]}, {ia[2], ia[3]}, {ib[0], ib[1]}, {ib[2], ib[3]}};
-                const float xs[2] = {s4.x, s4.z};
-                const float gs[2] = {s4.y, s4.w};
-                float wmf[4] = {0.f, 0.f, 0.f, 0.f};
-                if (QTYPE == 1) {
-                    const float2 wm01 = __half22float2(*reinterpret_cast<const __half2*>(&st.wm[i].x));
-                    const float2 wm23 = __half22float2(*reinterpret_cast<const __half2*>(&st.wm[i].y));
-                    wmf[0] = wm01.x, wmf[1] = wm01.y, wmf[2] = wm23.x, wmf[3] = wm23.y;
-                }
-    #pragma unroll
-                for (int c = 0; c < 4; c++) {
-    #pragma unroll
-                    for (int mi = 0; mi < 2; mi++) {
-                        int I = iv[c][mi];
-                        if (SIGNED) I -= __float_as_int(gs[mi]);
-                        acc[c][mi] = fmaf(__fmul_rn(wdf[c], xs[mi]), (float)I, acc[c][mi]);
-                        if (QTYPE == 1) acc[c][mi] = fmaf(wmf[c], gs[mi], acc[c][mi]);
-                    }
-                }
+                // the block arithmetic every decode kernel shares (exact integer sums, then the fp32 scaling)
+                block_accumulate<G, QTYPE, SIGNED>(st.q[i], st.wd[i], st.wm[i], my_codes + (int64_t)kb * G, row_live,
+                                                   sc + kb * 16, t, acc);
                 // advance; close the segment at a stripe boundary
                 kb++;
                 if (kb == p.Kg) {
