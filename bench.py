@@ -848,7 +848,7 @@ def our_arm(args) -> int:
                          "traffic": (DECODE_TRAFFIC_RATIO * per_rank_algo / n_fc_launches) if not distributed else None,
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the step's FC launches "
                                            "(summary under profiles/), per launch",
-                         "peak_kind": peak_kind, "kernel": "fc_decode_ring_kernel<128,1,false,8,false,true>",
+                         "peak_kind": peak_kind, "kernel": "fc_decode_ring_kernel<128,1,false,ROWS,false,true> (ROWS = 1 for the one-row launch, 8 for the others)",
                          "algorithmic_bytes_per_step": per_rank_algo, "launches_per_step": n_fc_launches,
                          "algorithmic_bytes_per_launch": per_rank_algo / n_fc_launches,
                          "avg_launch_ms": ms_fc / n_fc_launches,
