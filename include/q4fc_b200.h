@@ -348,7 +348,10 @@ int q4fc_tp_collect_multi(const unsigned long long* const* stamped, const int64_
  * q4fc_quant_x_q8 followed by q4fc_fc_decode_multi (same codes bit for bit; outputs within rounding of the fp32 sums).
  *
  *   q4fc_fc_chain_create   checks the steps, uploads their tables (cudaMalloc + synchronous copies: not inside a
- *                          stream capture) and returns a handle bound to the current device.
+ *                          stream capture) and returns a handle bound to the current device.  The quantized input
+ *                          of a step (rows x largest K bytes), the partial sums and the step tables share an SM's
+ *                          shared memory with the weight ring: Q4FC_ELIMIT when less than two ring slots would be
+ *                          left (a 32-layer Llama-7B chain fits with up to 4 rows), or when the tables exceed 40 KB.
  *   q4fc_fc_chain_run      one cooperative launch of one CTA per SM on `stream`; asynchronous; may be captured into
  *                          a CUDA graph.  Launches of one handle must not overlap on the GPU.
  *   q4fc_fc_chain_check    host-synchronous: Q4FC_OK, or Q4FC_EDEVICE when a bounded wait inside a launch ran out
