@@ -600,47 +600,46 @@ def our_arm(args) -> int:
                                    "(q/k/v and gate/up one launch each), the second figure adds rmsnorm, residual adds "
                                    "and silu*up between the FCs")
             else:
-                tok_sched = tp.TPSchedule(arena) if fused else None
+                if fused:
+                    from llama_cl_b200.stack import FusedTPDecodeFCStack
 
-                def mk(w, N_):
-                    if fused:
-                        return tp.FusedTPLinearQ4(tok_sched, w, N_, max_rows=1, pdl=True)
-                    return tp.TPLinearQ4(w, N_, pdl=True, path="decode")
+                    tst = FusedTPDecodeFCStack(arena, layers, lm_head, hidden=H, intermediate=I, vocab=V, rows=1)
+                    tst.forward(h0, sync=True)
 
-                lay = [{nm: mk(l[nm], N_) for nm, N_, _ in names} for l in layers]
-                head = mk(lm_head, V)
-                logits = torch.empty((1, 1, V), device=dev, dtype=torch.float32)
+                    def run_tok() -> None:
+                        # the stack replays on a stream of its own: tie it to the stream the timing events are on
+                        cur = torch.cuda.current_stream(dev)
+                        tst.stream.wait_stream(cur)
+                        tst.forward()
+                        cur.wait_stream(tst.stream)
 
-                def token() -> None:
-                    # the seven FCs of chatllama/main.py:348-370 with their data dependences (q, k, v and gate, up as
-                    # one launch each); the non-FC ops between them are not part of this path
-                    h = h0
-                    if fused:
-                        tok_sched.step_begin()
+                else:
+                    def mk(w, N_):
+                        return tp.TPLinearQ4(w, N_, pdl=True, path="decode")
+
+                    lay = [{nm: mk(l[nm], N_) for nm, N_, _ in names} for l in layers]
+                    head = mk(lm_head, V)
+
+                    def run_tok() -> None:
+                        # the seven FCs of chatllama/main.py:348-370 with their data dependences; the non-FC ops
+                        # between them are not part of this path
+                        h = h0
                         for f in lay:
-                            q, _, _ = tp.fused_multi([f["q"], f["k"], f["v"]], h)
+                            q = f["q"](h)
+                            f["k"](h)
+                            f["v"](h)
                             o = f["o"](q)
-                            g_, _ = tp.fused_multi([f["gate"], f["up"]], o)
+                            g_ = f["gate"](o)
+                            f["up"](o)
                             h = f["down"](g_)
-                        head(h).tensor(out=logits)  # the token is done when every rank holds the whole logits row
-                        return
-                    for f in lay:
-                        q = f["q"](h)
-                        f["k"](h)
-                        f["v"](h)
-                        o = f["o"](q)
-                        g_ = f["gate"](o)
-                        f["up"](o)
-                        h = f["down"](g_)
-                    head(h)
+                        head(h)
 
-                run_tok = capture(token) if fused else token
                 ms_tok, _ = timed(run_tok, max(3, min(args.steps * inner, 60)))
                 stack["ms_per_token"] = ms_tok
                 stack["weight_gb_s"] = full_bytes / (ms_tok * 1e-3) / 1e9
-                stack["launch"] = ("cuda graph of one token (225 fused N-split FCs in 129 launches)" if fused
+                stack["launch"] = ("stack.FusedTPDecodeFCStack: cuda graph of one token (225 fused N-split FCs in 129 "
+                                   "launches + step barrier + one unpacking launch)" if fused
                                    else "eager, NCCL all-gather per FC")
-                del lay, head
             del layers, lm_head
         except Exception as e:
             stack = {"error": str(e)}

@@ -213,3 +213,67 @@ class DecodeFCStack:
 
     def weight_bytes(self) -> int:
         return sum(w.numel() for l in self.layers for w in (l[k] for k in LAYER_FCS)) + self.lm_head.numel()
+
+
+class FusedTPDecodeFCStack:
+    """The FC-only per-token schedule (``DecodeFCStack(glue="none")``) with every weight split along N over the
+    ranks of a process group: per layer q, k, v (one launch) | o | gate, up (one launch) | down, then lm_head, each
+    FC storing its columns, stamped, into every rank's buffer over NVLink and the next FC reading them from there
+    (``tp.FusedTPLinearQ4``) -- no collective call between the FCs.  One step barrier in front, one unpacking launch
+    for the logits at the end; captured once as a CUDA graph and replayed.  Every rank constructs it with its shards
+    of the same weights and calls ``forward`` with the same input.
+
+    ``layers[i]``: this rank's packed shards (``tp.shard_packed`` or packed from ``tp.shard_rows``) under the keys
+    q, k, v, o, gate, up, down; ``lm_head``: this rank's shard."""
+
+    def __init__(self, arena, layers: list[dict], lm_head: torch.Tensor, *, hidden: int, intermediate: int, vocab: int,
+                 rows: int = 1, graph: bool = True) -> None:
+        from . import tp
+
+        if not 1 <= rows <= 8:
+            raise RuntimeError("FusedTPDecodeFCStack serves decode steps: 1 <= rows <= 8")
+        self._tp = tp
+        self.arena, self.device = arena, arena.device
+        self.H, self.I, self.V, self.rows = hidden, intermediate, vocab, rows
+        self.schedule = tp.TPSchedule(arena)
+        widths = dict(q=hidden, k=hidden, v=hidden, o=hidden, gate=intermediate, up=intermediate, down=hidden)
+        self.layers = [{k: tp.FusedTPLinearQ4(self.schedule, l[k], widths[k], max_rows=rows, pdl=True) for k in LAYER_FCS}
+                       for l in layers]
+        self.head = tp.FusedTPLinearQ4(self.schedule, lm_head, vocab, max_rows=rows, pdl=True)
+        self.x = torch.zeros((1, rows, hidden), dtype=torch.float32, device=self.device)
+        self.logits = torch.empty((1, rows, vocab), dtype=torch.float32, device=self.device)
+        self.stream = torch.cuda.Stream(self.device)
+        self.use_graph, self._graph = bool(graph), None
+        self.launches_per_token = 4 * len(layers) + 3  # step barrier, 4 per layer, lm_head, unpacking
+
+    def enqueue(self) -> None:
+        """One token's schedule on the arena's current stream (what the graph holds)."""
+        tp, h = self._tp, self.x
+        self.schedule.step_begin()
+        for f in self.layers:
+            q, _, _ = tp.fused_multi([f["q"], f["k"], f["v"]], h)
+            o = f["o"](q)
+            g, _ = tp.fused_multi([f["gate"], f["up"]], o)
+            h = f["down"](g)
+        self.head(h).tensor(out=self.logits)  # the token is done when every rank holds the whole logits row
+
+    def forward(self, x: torch.Tensor | None = None, sync: bool = False) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            if x is not None:
+                self.x.copy_(x, non_blocking=True)
+            if not self.use_graph:
+                self.enqueue()
+            else:
+                if self._graph is None:
+                    self.enqueue()  # eager once on every rank (the step barrier pairs up), then capture
+                    self.stream.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=self.stream):
+                        self.enqueue()
+                    self._graph = g
+                self._graph.replay()
+        if sync:
+            self.stream.synchronize()
+        return self.logits
+
+    __call__ = forward

@@ -236,6 +236,27 @@ def _fused_worker(rank, world, initfile, result_q):
             for (nm, M), xh, y in zip(same, xs, ys):
                 ref = torch.from_numpy(cpu.restated.fc(xh.numpy(), full_np[nm], specs[nm][0]))
                 expect(torch.allclose(y, ref, rtol=1e-3, atol=1e-4), f"HostFusedBatch {nm} M={M} step {step}")
+        # the per-token FC schedule over N-split weights as a package class: one layer + lm_head, replayed as a graph,
+        # against the single-GPU stack on the full weights (same codes; the sums may meet in another order)
+        from llama_cl_b200.stack import DecodeFCStack, FusedTPDecodeFCStack
+
+        Hs, Is, Vs = 512, 1408, 1000
+        gs_ = torch.Generator().manual_seed(4242)
+        fullw = {k: pkg.llmops.offline_FC_quant_Q4A((torch.randn(n_, k_, generator=gs_) * 0.05).to(dev), qtype="q4_1",
+                                                    group_k=128)
+                 for k, (n_, k_) in dict(q=(Hs, Hs), k=(Hs, Hs), v=(Hs, Hs), o=(Hs, Hs), gate=(Is, Hs), up=(Is, Hs),
+                                         down=(Hs, Is), lm=(Vs, Hs)).items()}
+        shard = {k: tp.shard_packed(w, world, rank) for k, w in fullw.items()}
+        ref_stack = DecodeFCStack([{k: fullw[k] for k in ("q", "k", "v", "o", "gate", "up", "down")}], fullw["lm"],
+                                  hidden=Hs, intermediate=Is, vocab=Vs, rows=2, glue="none")
+        tp_stack = FusedTPDecodeFCStack(arena, [{k: shard[k] for k in ("q", "k", "v", "o", "gate", "up", "down")}],
+                                        shard["lm"], hidden=Hs, intermediate=Is, vocab=Vs, rows=2)
+        for step in range(3):
+            xt = torch.randn(1, 2, Hs, generator=gs_).to(dev)
+            want_l = ref_stack.forward(xt, sync=True)
+            got_l = tp_stack.forward(xt, sync=True)
+            scale_l = want_l.abs().max().item()
+            expect((want_l - got_l).abs().max().item() <= 0.02 * scale_l, f"FusedTPDecodeFCStack step {step}")
         outs = chain(xg)  # and the first schedule is undisturbed by it
         torch.cuda.synchronize()
         verify(xg, outs, "after the solo schedule")
